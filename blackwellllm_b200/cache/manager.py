@@ -6,7 +6,9 @@ window).  Each group has its own page pool, its own free list and, per request,
 its own block table; a page id indexes the same page in every layer of its group
 (as one page id does across all layers in the reference,
 src/core/paging/paged_kv_cache.h:74-78,96-107).  A pool is one tensor
-``[entries, 2, num_pages, num_kv_heads, page_size, head_dim]`` (2: keys, values).
+``[entries, 2, num_pages, num_kv_heads, page_size, head_dim]`` (2: keys, values; 1 where a mixer's values are
+part of its key rows).  A schedule entry may ask for several things at once (a tuple of requests: pages for its
+mixer, a state for the block around it); its view is then a tuple in the same order.
 
 A request gets pages when it grows (:meth:`CacheManager.append`, all or nothing
 across all groups), gives back the pages that a window has passed
@@ -30,7 +32,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..parts.base import FixedStateRequest, PagedKVRequest
+from ..parts.base import FixedStateRequest, PagedKVRequest, flatten_cache_requests
 from .pages import OutOfPages
 
 _c_int_p = ctypes.POINTER(ctypes.c_int)
@@ -58,7 +60,7 @@ def native():
                 "bwh_free_request": (ci, [vp, ci]), "bwh_num_blocks": (ci, [vp, ci, ci]),
                 "bwh_blocks": (ci, [vp, ci, ci, vp, ci]), "bwh_check": (ci, [vp]),
                 "bwh_pack_step": (ll, [vp, ci, vp, vp, vp, vp, vp, ci, ci, ll, vp, ll, vp, vp]),
-                "bwh_release_passed_many": (ci, [vp, ci, vp])}
+                "bwh_release_passed_many": (ci, [vp, ci, vp]), "bwh_set_keep_first": (ci, [vp, ci, ci])}
         for name, (res, args) in sigs.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
@@ -84,7 +86,7 @@ class StateView:
 @dataclass
 class _Group:
     request: PagedKVRequest
-    entries: List[int]
+    entries: List[int]              # the schedule entries whose pages lie in this pool, in pool order
     num_pages: int
     pool: Optional[torch.Tensor] = None
 
@@ -122,13 +124,19 @@ class CacheManager:
         self.groups: List[_Group] = []
         self.views: List[object] = [None] * len(requests)
         self._states: List[StateView] = []
+        # a schedule entry may ask for several things (a tuple): its view is then a tuple in the same order
+        flat = [(pos, k, rq) for pos, entry in enumerate(requests) for k, rq in enumerate(flatten_cache_requests(entry))]
+        made: Dict[tuple, object] = {}
         by_key: Dict[PagedKVRequest, int] = {}
-        for pos, rq in enumerate(requests):
+        keys_of: Dict[int, list] = {}
+        for pos, k, rq in flat:
             if isinstance(rq, PagedKVRequest):
                 if rq not in by_key:
                     by_key[rq] = len(self.groups)
                     self.groups.append(_Group(rq, [], 0))
+                    keys_of[by_key[rq]] = []
                 self.groups[by_key[rq]].entries.append(pos)
+                keys_of[by_key[rq]].append((pos, k))
         counts = [num_pages] * len(self.groups) if isinstance(num_pages, int) else list(num_pages)
         if len(counts) != len(self.groups):
             raise ValueError(f"{len(self.groups)} cache groups but {len(counts)} page counts")
@@ -137,26 +145,35 @@ class CacheManager:
                 raise ValueError("a page pool needs at least one page")
             grp.num_pages = int(n)
             r = grp.request
+            planes = 1 if r.single_plane else 2
             if device is not None:
-                grp.pool = torch.zeros((len(grp.entries), 2, n, r.num_kv_heads, page_size, r.head_dim),
+                grp.pool = torch.zeros((len(grp.entries), planes, n, r.num_kv_heads, page_size, r.head_dim),
                                        dtype=dtype, device=device)
-            for i, pos in enumerate(grp.entries):
-                self.views[pos] = PagedKVView(g, None if grp.pool is None else grp.pool[i, 0],
-                                              None if grp.pool is None else grp.pool[i, 1], page_size)
-        for pos, rq in enumerate(requests):
+            for i, key in enumerate(keys_of[g]):
+                made[key] = PagedKVView(g, None if grp.pool is None else grp.pool[i, 0],
+                                        None if grp.pool is None else grp.pool[i, planes - 1], page_size)
+        for pos, k, rq in flat:
             if isinstance(rq, FixedStateRequest):
                 st = None if device is None else torch.zeros((max_requests, *rq.shape), dtype=rq.dtype,
                                                              device=device)
-                self.views[pos] = StateView(st)
-                self._states.append(self.views[pos])
-            elif rq is not None and not isinstance(rq, PagedKVRequest):
+                made[(pos, k)] = StateView(st)
+                self._states.append(made[(pos, k)])
+            elif not isinstance(rq, PagedKVRequest):
                 raise TypeError(f"schedule entry {pos}: unknown cache request {rq!r}")
+        for pos, entry in enumerate(requests):
+            if isinstance(entry, (tuple, list)):
+                self.views[pos] = tuple(made[(pos, k)] for k in range(len(flatten_cache_requests(entry))))
+            elif entry is not None:
+                self.views[pos] = made[(pos, 0)]
         G = len(self.groups)
         windows = (ctypes.c_int * max(G, 1))(*[int(g.request.window or 0) for g in self.groups])
         pages = (ctypes.c_int * max(G, 1))(*[g.num_pages for g in self.groups])
         self._h = native().bwh_create(G, windows, pages, page_size, max_requests)
         if not self._h:
             raise ValueError("the host runtime refused the cache sizes")
+        for gi, g in enumerate(self.groups):
+            if g.request.keep_first:
+                native().bwh_set_keep_first(self._h, gi, int(g.request.keep_first))
         self._handles: Dict[object, int] = {}
         self._scratch = (ctypes.c_int * max(G, 1))()
         self.slots = _Slots(self)

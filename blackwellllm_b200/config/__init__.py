@@ -6,3 +6,4 @@ from .specs import (AttentionSpec, DenseMLPSpec, GatedLinearAttentionSpec, Hyper
 from ..models import dense_decoder as _dense_decoder  # noqa: F401  (registers Llama and Qwen2)
 from ..models import gafulix as _gafulix  # noqa: F401  (registers Gafulix)
 from ..models import fuvevik as _fuvevik  # noqa: F401  (registers Fuvevik)
+from ..models import zigipel as _zigipel  # noqa: F401  (registers Zigipel)

@@ -117,6 +117,37 @@ class AttentionSpec:
     sink: bool = False
     output_gate: bool = False
     shares_kv: bool = False
+    # ``gate_per_head``: the output gate has ONE number per query head (tensor "g" is [heads, hidden]) instead of one
+    # per channel.  ``v_norm_eps``: every value head is divided by sqrt(mean(v^2) + eps) before it is cached (no
+    # gain).  ``distance_bias``: r1_h ln(1 + r2_h (i - j)) is taken off the score of query i and key j, with two
+    # learned numbers per query head (tensors "r1", "r2").  ``keep_first``: with a window, the first so many keys of
+    # a sequence stay visible to every later query.
+    gate_per_head: bool = False
+    v_norm_eps: Optional[float] = None
+    distance_bias: bool = False
+    keep_first: int = 0
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose keys and values of all heads are made from one latent vector per token:
+    ``[c_raw, k_rot] = W_dkv x`` (``kv_rank`` + ``rot_dim`` rows), ``c = rms_norm(c_raw) * gain``; head h has the key
+    ``[W_uk,h c, rotated k_rot]`` and the value ``W_uv,h c``; its query ``W_q,h x`` is laid out as ``head_dim`` plain
+    channels, then ``rot_dim`` rotated ones.  Only c and the rotated k_rot are cached.  ``position``: the rotary
+    encoding of the rotated parts (its ``rotary_dim`` = ``rot_dim``).  ``window``, ``sink``, ``softmax_scale`` as in
+    :class:`AttentionSpec`.  ``names``: (role, name) pairs for q, dkv, dkv_norm, uk, uv, o, sink."""
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    kv_rank: int
+    norm_eps: float
+    position: Any
+    softmax_scale: float
+    window: Optional[int] = None
+    sink: bool = False
+    kind: str = "latent_attention"
+    names: Tuple[Tuple[str, str], ...] = ()
 
 
 @dataclass(frozen=True)
@@ -179,6 +210,9 @@ class SwiGLUSpec:
     act_limit: float = 0.0
     act_alpha: float = 1.0
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+    # ``activation`` "gelu_tanh": 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u.  ``bias_names``: the three
+    # projections' bias vectors (gate, up, down), or None for projections without biases.
+    bias_names: Optional[Tuple[str, str, str]] = None
 
 
 @dataclass(frozen=True)
@@ -207,7 +241,8 @@ class LayerSpec:
 
     ``block`` names the arrangement (``"prenorm"``: x += mixer(norm(x));
     x += ffn(norm(x)); ``"sandwich"``: the same with a second norm on each sublayer's output; ``"hyper"``:
-    pre-norm sublayers over several copies of the stream, see ``hyper``).  ``ffn`` may be ``None`` for a mixer-only layer.
+    pre-norm sublayers over several copies of the stream, see ``hyper``; ``"parallel"``: one norm whose output both
+    sublayers read, see ``token_shift``).  ``ffn`` may be ``None`` for a mixer-only layer.
     """
     mixer: Any
     ffn: Any
@@ -227,6 +262,10 @@ class LayerSpec:
     ffn_post_norm_prefix: str = ""
     # the "hyper" arrangement keeps several copies of the stream (a :class:`HyperConnectionSpec`)
     hyper: Any = None
+    # the "parallel" arrangement: ONE norm, both sublayers read its output, x += mixer(h) + ffn(h).  ``token_shift``:
+    # the name of a vector s [hidden]; the mixer then reads h_t + (h_{t-1} - h_t) * s (zeros before a sequence's first
+    # token; the feed-forward reads h_t as it is), and the block keeps h of a request's last token between steps.
+    token_shift: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -240,6 +279,30 @@ class ScheduleEntry:
     # the embedding's output (the stream as it was before the first run) is added to the stream right
     # before this run: the start of a repeated pass over a stretch of layers
     add_embedding: bool = False
+    # the number t of the pass that this run opens (None: it opens none): right before it the stream becomes
+    # W [x; x0] + step[t], x0 the embedding's output (:class:`PassInputSpec` of the model)
+    pass_input: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class BigramEmbeddingSpec:
+    """A second table added to the embedding's output: row ``(previous token * mul_prev + token * mul_cur) mod
+    buckets`` of a tensor [buckets + 1, hidden]; a sequence's first token takes the last row.  The engine keeps a
+    request's last token between steps."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    name: str = "bigram"
+
+
+@dataclass(frozen=True)
+class PassInputSpec:
+    """What happens to the stream before every pass over a repeated stretch of layers (the first pass too):
+    ``x <- W [x; x0] + step[t]``, W [hidden, 2 hidden] with the columns for x first, x0 the embedding's output,
+    step [times, hidden], t the number of the pass."""
+    times: int
+    weight: str = "loop.in"
+    step: str = "loop.step"
 
 
 @dataclass(frozen=True)
@@ -267,6 +330,10 @@ class ModelConfig:
     # number of copies the stream is kept in (None: one plain stream; a number: every layer is a "hyper" block)
     position_embedding: Any = None
     streams: Optional[int] = None
+    # a hashed table of token pairs added to the embedding (:class:`BigramEmbeddingSpec`), and the mixing of the stream
+    # with the embedding's output before every pass of a repeated stretch (:class:`PassInputSpec`)
+    bigram_embedding: Any = None
+    pass_input: Any = None
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
     stored_dtype: str = "bfloat16"

@@ -23,7 +23,8 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
                       const int* __restrict__ req_of_token, const int* __restrict__ block_table,
                       int max_blocks, OT* __restrict__ out, int nh, int nkv, int hd, int page_size,
                       int num_pages, int window, int chunk, float scale, const float* __restrict__ sink,
-                      const float* __restrict__ gate, long long gate_ld, int gate_dv) {
+                      const float* __restrict__ gate, long long gate_ld, int gate_dv,
+                      const float* __restrict__ dist, int keep_first) {
     extern __shared__ float smem[];
     float* qs = smem;                       // [hd]
     float* accs = qs + hd;                  // [WARPS][hd]
@@ -35,7 +36,10 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
     const int r = req_of_token[t];
     const int* bt = block_table + (size_t)r * max_blocks;
     const int lo = bw::first_visible(q_pos, window, chunk);
-    const int n_keys = q_pos - lo + 1;
+    // the keys a row walks: the kept first keys that lie before the window, then the window's
+    const int n_kept = keep_first < lo ? (keep_first > 0 ? keep_first : 0) : lo;
+    const int n_keys = n_kept + q_pos - lo + 1;
+    const float r1 = dist ? dist[h] : 0.f, r2 = dist ? dist[nh + h] : 0.f;
 
     for (int c = threadIdx.x; c < hd; c += blockDim.x)
         qs[c] = bw::to_f32(q[((size_t)t * nh + h) * hd + c]);
@@ -48,7 +52,8 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
 
     const int n_chunks = (n_keys + 31) / 32;
     for (int ch = warp; ch < n_chunks; ch += WARPS) {
-        const int kp = lo + ch * 32 + lane;          // this lane's key position
+        const int kn = ch * 32 + lane;               // this lane's key, counted along the row's walk
+        const int kp = kn < n_kept ? kn : lo + (kn - n_kept);
         const bool valid = kp <= q_pos;
         float s = -INFINITY;
         size_t row_off = 0;
@@ -60,6 +65,7 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
                 float d = 0.f;
                 for (int c = 0; c < hd; ++c) d = fmaf(qs[c], bw::to_f32(kr[c]), d);
                 s = d * scale;
+                if (dist) s -= bw::distance_bias(r1, r2, q_pos - kp);
             }
         }
         const float cm = bw::warp_max(s);
@@ -113,11 +119,14 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
 // gate: float32 [T, >= nh * gate_dv], rows gate_ld apart, or null: output channel c < gate_dv of (token, head) is
 // multiplied by sigmoid(gate[token, head * gate_dv + c]); channels from gate_dv on become zero.
 // type: element type of q, the pages and out (all the same).  window <= 0: no window; chunk <= 0: no blocks (bw::first_visible).
+// dist: float32 [2, nh] (r1 of every head, then r2) or null: r1 ln(1 + r2 (query position - key position)) is taken off
+// every score.  keep_first: the first so many keys of a sequence stay visible whatever the window says.  gate_dv < 0:
+// one gate number per head (bw::out_gate).
 BW_EXPORT int bw_attention_simt(const void* q, const void* k_pages, const void* v_pages, int type,
                                 const int* positions, const int* req_of_token, const int* block_table,
                                 int max_blocks, void* out, int T, int nh, int nkv, int hd, int page_size,
                                 int num_pages, int window, int chunk, float scale, const float* sink, const float* gate,
-                                long long gate_ld, int gate_dv, void* stream) {
+                                long long gate_ld, int gate_dv, const float* dist, int keep_first, void* stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 32 * MAX_CH || nkv <= 0 || nh % nkv != 0) return BW_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -126,11 +135,11 @@ BW_EXPORT int bw_attention_simt(const void* q, const void* k_pages, const void* 
     if (type == BW_F32)
         attention_simt_kernel<float, float, float><<<grid, WARPS * 32, smem, s>>>(
             (const float*)q, (const float*)k_pages, (const float*)v_pages, positions, req_of_token,
-            block_table, max_blocks, (float*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv);
+            block_table, max_blocks, (float*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv, dist, keep_first);
     else if (type == BW_BF16)
         attention_simt_kernel<bf16, bf16, bf16><<<grid, WARPS * 32, smem, s>>>(
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, positions, req_of_token,
-            block_table, max_blocks, (bf16*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv);
+            block_table, max_blocks, (bf16*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv, dist, keep_first);
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;

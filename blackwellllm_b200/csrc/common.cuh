@@ -23,9 +23,11 @@
 //   BW_ACT_SILU           gated:  silu(g) * u
 //   BW_ACT_CLAMPED_SWISH  gated:  g' = min(g, limit), u' = clamp(u, -limit, limit):  g' sigmoid(alpha g') (u' + 1)
 //   BW_ACT_RELU2          no gate: max(x, 0)^2
+//   BW_ACT_GELU_TANH      gated:  0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u
 #define BW_ACT_SILU 0
 #define BW_ACT_CLAMPED_SWISH 1
 #define BW_ACT_RELU2 2
+#define BW_ACT_GELU_TANH 3
 
 // Programmatic dependent launch: a kernel launched through bw::launch may start while the kernel
 // before it in the stream is still draining.  Such a kernel calls BW_PDL_TRIGGER() early (the next
@@ -119,6 +121,17 @@ __host__ __device__ __forceinline__ int first_visible(int q_pos, int window, int
     return lo;
 }
 
+// What a query at q_pos sees of the key at k_pos <= q_pos: the keys from first_visible(...) on, and the first
+// `keep_first` keys of the sequence whatever the window says (0: none are kept).
+__host__ __device__ __forceinline__ bool key_visible(int k_pos, int lo, int keep_first) {
+    return k_pos >= lo || k_pos < keep_first;
+}
+
+// The distance bias that is taken off a score: r1 ln(1 + r2 (q_pos - k_pos)), r1 and r2 numbers of the query head.
+__device__ __forceinline__ float distance_bias(float r1, float r2, int dist) {
+    return r1 * log1pf(r2 * (float)dist);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);   // lo in the low half
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -137,6 +150,7 @@ __device__ __forceinline__ float glu(int act, float g, float u, float limit, flo
         u = fminf(fmaxf(u, -limit), limit);
         return g / (1.f + expf(-alpha * g)) * (u + 1.f);
     }
+    if (act == BW_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
     return g / (1.f + expf(-g)) * u;
 }
 __device__ __forceinline__ float unary_act(int act, float x) {
@@ -145,9 +159,11 @@ __device__ __forceinline__ float unary_act(int act, float x) {
 }
 
 // The output gate of an attention mixer: sigmoid(gate[token, head * dv + c]) for c < dv, 0 for the pad channels beyond
-// dv, 1 without a gate.  gate: float32 rows `ld` apart.
+// dv, 1 without a gate.  gate: float32 rows `ld` apart.  dv < 0: the gate has ONE number per head, gate[token, head],
+// for the head's first -dv channels.
 __device__ __forceinline__ float out_gate(const float* __restrict__ gate, long long ld, int dv, size_t token, int head, int c) {
     if (!gate) return 1.f;
+    if (dv < 0) return c < -dv ? 1.f / (1.f + expf(-gate[token * (size_t)ld + (size_t)head])) : 0.f;
     if (c >= dv) return 0.f;
     return 1.f / (1.f + expf(-gate[token * (size_t)ld + (size_t)head * dv + c]));
 }

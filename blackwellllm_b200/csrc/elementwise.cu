@@ -588,10 +588,10 @@ BW_EXPORT int bw_swiglu(const void* gu, int in_type, void* out, int out_type, in
     return launch_glu(gu, in_type, out, out_type, T, I, BW_ACT_SILU, 0.f, 1.f, stream);
 }
 
-// act: a gated activation of common.cuh (BW_ACT_SILU, BW_ACT_CLAMPED_SWISH with its limit and alpha)
+// act: a gated activation of common.cuh (BW_ACT_SILU, BW_ACT_CLAMPED_SWISH with its limit and alpha, BW_ACT_GELU_TANH)
 BW_EXPORT int bw_glu(const void* gu, int in_type, void* out, int out_type, int T, int I, int act, float limit, float alpha,
                      void* stream) {
-    if (act != BW_ACT_SILU && act != BW_ACT_CLAMPED_SWISH) return BW_ERR_BAD_ARG;
+    if (act != BW_ACT_SILU && act != BW_ACT_CLAMPED_SWISH && act != BW_ACT_GELU_TANH) return BW_ERR_BAD_ARG;
     return launch_glu(gu, in_type, out, out_type, T, I, act, limit, alpha, stream);
 }
 

@@ -25,6 +25,7 @@ enum : int {
 
 struct Group {
     int window = 0;                 // 0: every key is kept
+    int keep_first = 0;             // with a window: the first so many keys of a request stay needed
     int num_pages = 0;
     std::vector<int> free;          // LIFO: back() is handed out next
     std::vector<uint8_t> is_free;
@@ -178,6 +179,14 @@ BWH_EXPORT long long bwh_append(void* cache, int h, long long n_new) {
     return old;
 }
 
+// The first n keys of every request stay needed in this group, whatever its window says (n <= 0: none).
+BWH_EXPORT int bwh_set_keep_first(void* cache, int group, int n) {
+    Cache* c = (Cache*)cache;
+    if (!c || group < 0 || group >= (int)c->groups.size()) return BWH_BAD_ARG;
+    c->groups[group].keep_first = n > 0 ? n : 0;
+    return BWH_OK;
+}
+
 // Gives back the pages that every later query's window has passed; returns how many.
 BWH_EXPORT int bwh_release_passed(void* cache, int h) {
     Cache* c = (Cache*)cache;
@@ -189,7 +198,8 @@ BWH_EXPORT int bwh_release_passed(void* cache, int h) {
         if (g.window <= 0) continue;
         const int keep_from = first_needed_block(c, g, r->length);   // the next query sits at position `length`
         int& first = r->first_live[gi];
-        for (int i = first; i < keep_from && i < (int)r->blocks[gi].size(); ++i) {
+        const int kept_blocks = (int)ceil_div(g.keep_first, c->page_size);   // never given back before the request ends
+        for (int i = first > kept_blocks ? first : kept_blocks; i < keep_from && i < (int)r->blocks[gi].size(); ++i) {
             int& p = r->blocks[gi][i];
             if (p >= 0) { const int rc = free_pages_of(g, &p, 1); if (rc) return rc; ++freed; p = -1; }
         }

@@ -110,7 +110,8 @@ head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __
                       const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
                       float q_coef, float q_every,
                       OT* __restrict__ q_out, OT* __restrict__ k_pages, OT* __restrict__ v_pages,
-                      int nh, int nkv, int dq, int dv, int dpad, int page_size, int num_pages, int has_kv, int vec) {
+                      int nh, int nkv, int dq, int dv, int dpad, int page_size, int num_pages, int has_kv, int vec,
+                      float v_eps) {
     BW_PDL_TRIGGER();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -176,6 +177,18 @@ head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __
             dst[c] = bw::from_f32<OT>(o);
         }
     }
+    if (page >= 0 && v_eps > 0.f) {
+        // every value head divided by its own root mean square (no gain): a warp per head
+        const float* vsrc = row + nq + nk;
+        for (int h = warp; h < nkv; h += nwarps) {
+            float ss = 0.f;
+            for (int c = lane; c < dv; c += 32) { const float v = vsrc[(size_t)h * dv + c]; ss = fmaf(v, v, ss); }
+            const float r = rsqrtf(bw::warp_sum(ss) / (float)dv + v_eps);
+            OT* dst = v_pages + (((size_t)page * nkv + h) * page_size + slot) * dpad;
+            for (int c = lane; c < dpad; c += 32) dst[c] = bw::from_f32<OT>(c < dv ? vsrc[(size_t)h * dv + c] * r : 0.f);
+        }
+        return;
+    }
     if (page >= 0) {
         const float* vsrc = row + nq + nk;
         if (vec) {
@@ -198,13 +211,14 @@ head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __
 
 // The per-head form (head_norm_rope_kernel).  ld: floats between rows of qkv; q_gain / k_gain: float32 [dq] or
 // null; q_coef, q_every: the queries' temperature (q_coef == 0: none; q_every > 0); has_kv == 0: the rows hold
-// no keys and values and nothing is appended.
+// no keys and values and nothing is appended.  v_eps > 0: every value head is divided by sqrt(mean(v^2) + v_eps) on its way
+// into the cache.
 BW_EXPORT int bw_head_norm_rope_append(const float* qkv, long long ld, const int* positions, const int* req_of_token,
                                        const int* block_table, int max_blocks, const float* table, int rotary_dim,
                                        int interleaved, const float* q_gain, const float* k_gain, float eps,
                                        float q_coef, float q_every, void* q_out, void* k_pages, void* v_pages,
                                        int out_type, int T, int nh, int nkv, int dq, int dv, int dpad, int page_size,
-                                       int num_pages, int has_kv, void* stream) {
+                                       int num_pages, int has_kv, float v_eps, void* stream) {
     if (T <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > dq || (rotary_dim & 1) || dq <= 0 || dv <= 0 || dpad < dq || dpad < dv ||
         nh <= 0 || nkv <= 0 || page_size <= 0 || (rotary_dim > 0 && !table) || (q_coef != 0.f && !(q_every > 0.f)) ||
@@ -215,7 +229,7 @@ BW_EXPORT int bw_head_norm_rope_append(const float* qkv, long long ld, const int
                     (((uintptr_t)qkv | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
 #define BW_HN(OT) bw::launch((head_norm_rope_kernel<OT>), dim3(T), dim3(256), 0, s, qkv, ld, positions, req_of_token, block_table, \
         max_blocks, table, rotary_dim, interleaved, q_gain, k_gain, eps, q_coef, q_every, (OT*)q_out, (OT*)k_pages, (OT*)v_pages, \
-        nh, nkv, dq, dv, dpad, page_size, num_pages, has_kv, vec)
+        nh, nkv, dq, dv, dpad, page_size, num_pages, has_kv, vec, v_eps)
     if (out_type == BW_F32) BW_HN(float);
     else if (out_type == BW_BF16) BW_HN(bf16);
     else return BW_ERR_BAD_ARG;

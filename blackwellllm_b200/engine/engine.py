@@ -28,7 +28,7 @@ from ..cache.pages import OutOfPages
 from ..config.registry import load_config, parse_config
 from ..config.specs import ModelConfig
 from ..models.decoder import DecoderModel
-from ..parts.base import BuildContext, PagedKVRequest
+from ..parts.base import BuildContext, PagedKVRequest, flatten_cache_requests
 from ..weights.loader import bind_tensors, load_weights
 from ..weights.random_init import random_tensors
 from .batch import BatchBuilder, StepBatch, StepEntry
@@ -154,13 +154,14 @@ class Engine:
         if o.max_tokens is not None:
             return max(1, -(-int(o.max_tokens) // o.page_size))
         groups: Dict[PagedKVRequest, int] = {}
-        for r in requests:
-            if isinstance(r, PagedKVRequest):
-                groups[r] = groups.get(r, 0) + 1
+        for entry in requests:
+            for r in flatten_cache_requests(entry):
+                if isinstance(r, PagedKVRequest):
+                    groups[r] = groups.get(r, 0) + 1
         if not groups:
             return 1
         esize = 4 if self.dtype == torch.float32 else 2
-        per_page = sum(n * 2 * r.num_kv_heads * o.page_size * r.head_dim * esize for r, n in groups.items())
+        per_page = sum(n * (1 if r.single_plane else 2) * r.num_kv_heads * o.page_size * r.head_dim * esize for r, n in groups.items())
         free, _ = torch.cuda.mem_get_info(self.device)
         return max(1, int(free * o.kv_fraction) // per_page)
 

@@ -312,14 +312,16 @@ def swiglu(gu: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.T
     return out
 
 
-ACT_SILU, ACT_CLAMPED_SWISH, ACT_RELU2 = 0, 1, 2   # the activation codes of csrc/common.cuh
-GATED_ACTIVATIONS = {"silu": ACT_SILU, "clamped_swish": ACT_CLAMPED_SWISH}
+ACT_SILU, ACT_CLAMPED_SWISH, ACT_RELU2, ACT_GELU_TANH = 0, 1, 2, 3   # the activation codes of csrc/common.cuh
+GATED_ACTIVATIONS = {"silu": ACT_SILU, "clamped_swish": ACT_CLAMPED_SWISH, "gelu_tanh": ACT_GELU_TANH}
 UNARY_ACTIVATIONS = {"relu2": ACT_RELU2}
+GEMM_TC_GATED_ACTIVATIONS = (ACT_SILU, ACT_CLAMPED_SWISH)   # what gemm_tc's fused gate/up epilogue computes
+GEMM_TC_GATED_BIAS = False                                  # ... and whether it takes biases on gate and up
 
 
 def glu(gu: torch.Tensor, act: int, limit: float = 0.0, alpha: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """[T, 2I] (gate | up) -> [T, I]: ACT_SILU ``silu(gate) * up``; ACT_CLAMPED_SWISH, with g = min(gate, limit) and
-    u = clamp(up, -limit, limit): ``g * sigmoid(alpha * g) * (u + 1)``.  Float32 arithmetic."""
+    u = clamp(up, -limit, limit): ``g * sigmoid(alpha * g) * (u + 1)``; ACT_GELU_TANH ``gelu_tanh(gate) * up``.  Float32 arithmetic."""
     _dev(gu, "gate_up")
     T, I2 = gu.shape
     if I2 % 2:
@@ -463,9 +465,11 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
 def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, positions: torch.Tensor,
                    req_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, window: Optional[int],
                    scale: float, out: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                   sink: Optional[torch.Tensor] = None, gate: Optional[tuple] = None) -> torch.Tensor:
+                   sink: Optional[torch.Tensor] = None, gate: Optional[tuple] = None,
+                   dist: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     _dev(q, "q"); _dev(k_pages, "k_pages", q.dtype); _dev(v_pages, "v_pages", q.dtype)
     _check_sink(sink, nh)
+    _check_dist(dist, nh)
     g, g_ld, g_dv = _gate_args(gate, q.shape[0], nh, k_pages.shape[3])
     _dev(positions, "positions", torch.int32); _dev(req_of_token, "req_of_token", torch.int32)
     _dev(block_table, "block_table", torch.int32)
@@ -477,20 +481,26 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
         out = torch.empty_like(q)
     fn = _fn("attention_simt", "bw_attention_simt",
              [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_ll, c_int, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q, "q"), _ptr(positions), _ptr(req_of_token),
               _ptr(block_table), block_table.shape[1], _ptr(out), T, nh, nkv, hd, page_size, num_pages,
-              int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _ptr(g), g_ld, g_dv, _stream()), "attention_simt")
+              int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _ptr(g), g_ld, g_dv, _ptr(dist),
+              int(keep_first or 0), _stream()), "attention_simt")
     return out
 
 
 def _gate_args(gate: Optional[tuple], T: int, nh: int, hd: int):
     """``gate`` = (float32 tensor [T, nh * dv], possibly a column range of a wider one; dv): what the attention
-    kernels take as pointer, row stride and value size."""
+    kernels take as pointer, row stride and value size.  (g [T, nh], dv, "head"): one number per head; the kernels
+    get the value size negated for it."""
     if gate is None:
         return None, 0, 0
-    g, dv = gate
+    g, dv = gate[0], gate[1]
     _dev(g, "gate", torch.float32, contiguous=False)
+    if len(gate) > 2 and gate[2] == "head":
+        if g.shape != (T, nh) or g.stride(1) != 1 or not 0 < dv <= hd:
+            raise KernelError(f"attention: a gate per head must be float32 [T, nh] with contiguous rows and dv <= {hd}")
+        return g, g.stride(0), -int(dv)
     if g.shape != (T, nh * dv) or g.stride(1) != 1 or not 0 < dv <= hd:
         raise KernelError(f"attention: the gate must be float32 [T, nh * dv] with contiguous rows and dv <= {hd}")
     return g, g.stride(0), int(dv)
@@ -501,6 +511,13 @@ def _check_sink(sink: Optional[torch.Tensor], nh: int) -> None:
         _dev(sink, "sink", torch.float32)
         if sink.numel() != nh:
             raise KernelError(f"attention: the sink must have one float32 entry per query head ({nh})")
+
+
+def _check_dist(dist: Optional[torch.Tensor], nh: int) -> None:
+    if dist is not None:
+        _dev(dist, "dist", torch.float32)
+        if tuple(dist.shape) != (2, nh):
+            raise KernelError(f"attention: the distance bias must be float32 [2, {nh}] (r1 of every head, then r2)")
 
 
 # ------------------------------------------------------------------ sampling
@@ -781,7 +798,8 @@ def attention_takes_unrotated(hd: int, page_size: int) -> bool:
 def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
                     block_table: torch.Tensor, nh: int, window: Optional[int], scale: float,
                     chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None,
-                    gate: Optional[tuple] = None) -> torch.Tensor:
+                    gate: Optional[tuple] = None, dist: Optional[torch.Tensor] = None,
+                    keep_first: int = 0) -> torch.Tensor:
     """Causal attention of the batch's tokens over the paged cache (which already
     holds this step's keys and values, unless ``q`` is an :class:`UnrotatedQKV`).  float32: the
     CUDA-core kernel; bfloat16: the tensor-core kernel built for this head size.  A query sees the keys
@@ -789,14 +807,21 @@ def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
     start of its own block of ``chunk`` positions (blocks are counted from position 0).  ``sink`` (float32, one
     entry per query head): the softmax of a row has one more term exp(sink) that has no key and no value.
     ``gate`` = (g float32 [T, nh * dv], dv): channel c < dv of every head's output is multiplied by
-    sigmoid(g[t, head * dv + c]) as it is written; channels from dv on (padding) become zero."""
+    sigmoid(g[t, head * dv + c]) as it is written; channels from dv on (padding) become zero; (g [T, nh], dv, "head"):
+    one gate number per head.  ``dist`` (float32 [2, nh]: r1 of every head, then r2): r1 ln(1 + r2 (i - j)) is taken off
+    the score of query position i and key position j.  ``keep_first``: the first so many keys of a sequence stay
+    visible beyond the window."""
     if isinstance(q, UnrotatedQKV):
         if batch.T == batch.R and attention_takes_unrotated(k_pages.shape[3], k_pages.shape[2]):
             return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate)
         q = q.materialise()
     if q.dtype == torch.float32:
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
-                              window, scale, chunk=chunk, sink=sink, gate=gate)
+                              window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first)
+    if dist is not None or keep_first or (gate is not None and len(gate) > 2):
+        # the tensor-core kernels know neither: the CUDA-core kernel in bfloat16
+        return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
+                              window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first)
     return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate)
 
 
@@ -1082,13 +1107,14 @@ def head_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, t
                           rotary_dim: int, interleaved: bool, q_gain: Optional[torch.Tensor],
                           k_gain: Optional[torch.Tensor], eps: float, k_pages: torch.Tensor, v_pages: torch.Tensor,
                           nh: int, nkv: int, dq: int, dv: int, has_kv: bool = True, append: bool = True,
-                          q_temp: Optional[tuple] = None) -> torch.Tensor:
+                          q_temp: Optional[tuple] = None, v_eps: float = 0.0) -> torch.Tensor:
     """:func:`qk_norm_rope_append` with the norm taken per head: every query head is divided by its own root mean
     square and multiplied by ``q_gain`` (float32 [dq], shared by the heads; ``k_gain`` for the key heads).
     ``qkv`` float32 [T, >= nh*dq (+ nkv*dq + nkv*dv with ``has_kv``)]: further columns (a gate's projection) are
     left alone.  ``q_temp`` = (coef, every): after norm and rotation the queries of a token at position p are
     multiplied by ``1 + coef * log(1 + n)``, n the whole periods of ``every`` positions in p + 1.  Without ``has_kv`` (a run that reads another
-    run's keys and values) nothing is appended."""
+    run's keys and values) nothing is appended.  ``v_eps`` > 0: every value head is divided by
+    sqrt(mean(v^2) + v_eps) on its way into the cache."""
     _dev(qkv, "qkv", torch.float32); _dev(block_table, "block_table", torch.int32)
     _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)
     T = qkv.shape[0]
@@ -1109,12 +1135,105 @@ def head_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, t
     q_out = torch.empty((T, nh * dpad), dtype=k_pages.dtype, device=qkv.device)
     fn = _fn("qk_norm_rope", "bw_head_norm_rope_append",
              [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float,
-              c_float, c_void_p, c_void_p, c_void_p] + [c_int] * 10 + [c_void_p])
+              c_float, c_void_p, c_void_p, c_void_p] + [c_int] * 10 + [c_float, c_void_p])
     _check(fn(_ptr(qkv), qkv.stride(0), _ptr(batch.positions), _ptr(batch.req_of_token), _ptr(block_table),
               block_table.shape[1], _ptr(table), int(rotary_dim), int(interleaved), _ptr(q_gain), _ptr(k_gain), float(eps),
               coef, every, _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _code(k_pages, "pages"), T, nh, nkv, dq, dv, dpad,
-              page_size, num_pages if (append and has_kv) else 0, int(has_kv), _stream()), "head_norm_rope_append")
+              page_size, num_pages if (append and has_kv) else 0, int(has_kv), float(v_eps or 0.0), _stream()),
+           "head_norm_rope_append")
     return q_out
+
+
+# ------------------------------------------------------------------ rows that look at the token before them
+
+def embed_bigram(table: torch.Tensor, second: torch.Tensor, batch, prev_token: torch.Tensor, buckets: int, mul_prev: int,
+                 mul_cur: int, scale: float = 1.0) -> torch.Tensor:
+    """float32 [T, H]: ``table[id] * scale + second[row]``, row = (previous token * mul_prev + id * mul_cur) mod
+    ``buckets``, or row ``buckets`` for a sequence's first token.  The previous token of a portion's first token comes
+    from ``prev_token`` (int32 [slots], indexed by the request's slot), which then takes the portion's last token."""
+    _dev(table, "table"); _dev(second, "second table", table.dtype); _dev(prev_token, "prev_token", torch.int32)
+    V, H = table.shape
+    if tuple(second.shape) != (buckets + 1, H) or buckets <= 0:
+        raise KernelError(f"embed_bigram: the second table must be [{buckets + 1}, {H}]")
+    out = torch.empty((batch.T, H), dtype=torch.float32, device=table.device)
+    fn = _fn("rowstate", "bw_embed_bigram", [c_void_p, c_void_p, c_int] + [c_void_p] * 7 + [c_int] * 4 + [c_ll, c_ll, c_float, c_void_p])
+    _check(fn(_ptr(table), _ptr(second), _code(table, "table"), _ptr(batch.token_ids), _ptr(batch.positions),
+              _ptr(batch.req_of_token), _ptr(batch.cu_q), _ptr(batch.state_slot), _ptr(prev_token), _ptr(out), batch.T, H, V,
+              int(buckets), int(mul_prev), int(mul_cur), float(scale), _stream()), "embed_bigram")
+    return out
+
+
+def rmsnorm_shift(x: torch.Tensor, gain: torch.Tensor, shift: torch.Tensor, state: torch.Tensor, batch, eps: float,
+                  out_dtype: torch.dtype, want_h: bool = True):
+    """(h, hs): ``h = x / rms(x) * gain`` and ``hs_t = h_t + (h_{t-1} - h_t) * shift`` with zeros before a sequence's
+    first token.  ``state`` (float32 [slots, H]) holds h of every request's last token so far: a portion's first token
+    reads it, and it takes the portion's last h.  ``want_h=False``: only hs is written (h is None)."""
+    _dev(x, "x", torch.float32); _dev(gain, "gain", torch.float32); _dev(shift, "shift", torch.float32)
+    _dev(state, "state", torch.float32)
+    T, H = x.shape
+    if gain.numel() != H or shift.numel() != H or state.dim() != 2 or state.shape[1] != H or T != batch.T:
+        raise KernelError("rmsnorm_shift: gain and shift [H], state [slots, H], one row of x per token of the batch")
+    h = torch.empty((T, H), dtype=out_dtype, device=x.device) if want_h else None
+    hs = torch.empty((T, H), dtype=out_dtype, device=x.device)
+    fn = _fn("rowstate", "bw_rmsnorm_shift", [c_void_p] * 10 + [c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(x), _ptr(gain), _ptr(shift), _ptr(state), _ptr(batch.positions), _ptr(batch.req_of_token),
+              _ptr(batch.cu_q), _ptr(batch.state_slot), _ptr(h), _ptr(hs), _code(hs, "out"), T, H, float(eps), _stream()),
+           "rmsnorm_shift")
+    return h, hs
+
+
+def concat2_cast(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """[T, 2H] in ``out_dtype``: the float32 tensors a and b [T, H] side by side."""
+    _dev(a, "a", torch.float32); _dev(b, "b", torch.float32)
+    if a.shape != b.shape or a.dim() != 2:
+        raise KernelError("concat2_cast: two float32 tensors [T, H]")
+    T, H = a.shape
+    out = torch.empty((T, 2 * H), dtype=out_dtype, device=a.device)
+    fn = _fn("rowstate", "bw_concat2_cast", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(a), _ptr(b), _ptr(out), _code(out, "out"), T, H, _stream()), "concat2_cast")
+    return out
+
+
+# ------------------------------------------------------------------ latent attention
+
+def latent_prep(proj: torch.Tensor, q_off: int, kv_off: int, batch, block_table: torch.Tensor, table: torch.Tensor,
+                c_gain: torch.Tensor, eps: float, k_pages: torch.Tensor, H: int, d: int, dr: int, rank: int,
+                append: bool = True) -> torch.Tensor:
+    """From the projections of a step (float32 [T, ...]: H query heads of d plain + dr rotated channels at column
+    ``q_off``; the latent's rank channels and the shared key part's dr channels at ``kv_off``): appends
+    [rms_norm(latent) * c_gain, rotated key part, zeros] to the tokens' cache rows and returns the queries
+    [T, H * dpad] with channels [rank, rank + dr) of every head filled (the rotated parts; channels [0, rank) are left
+    for :func:`headwise_linear`)."""
+    _dev(proj, "proj", torch.float32); _dev(block_table, "block_table", torch.int32); _dev(table, "table", torch.float32)
+    _dev(c_gain, "c_gain", torch.float32); _dev(k_pages, "k_pages")
+    T = proj.shape[0]
+    num_pages, nkv, page_size, dpad = k_pages.shape
+    if nkv != 1 or dpad < rank + dr or tuple(table.shape) != (T, dr) or c_gain.numel() != rank:
+        raise KernelError("latent_prep: pages [num_pages, 1, page, >= rank + dr], table [T, dr], gain [rank]")
+    q = torch.empty((T, H * dpad), dtype=k_pages.dtype, device=proj.device)
+    fn = _fn("latent", "bw_latent_prep", [c_void_p, c_ll, c_int, c_int] + [c_void_p] * 3 + [c_int, c_void_p, c_void_p, c_float,
+                                          c_void_p, c_void_p] + [c_int] * 9 + [c_void_p])
+    _check(fn(_ptr(proj), proj.stride(0), int(q_off), int(kv_off), _ptr(batch.positions), _ptr(batch.req_of_token),
+              _ptr(block_table), block_table.shape[1], _ptr(table), _ptr(c_gain), float(eps), _ptr(q), _ptr(k_pages),
+              _code(k_pages, "pages"), T, H, d, dr, rank, dpad, page_size, num_pages if append else 0, _stream()), "latent_prep")
+    return q
+
+
+def headwise_linear(x: torch.Tensor, x_off: int, x_hs: int, w: torch.Tensor, y: torch.Tensor, y_off: int, y_hs: int) -> torch.Tensor:
+    """``y[t, y_off + h * y_hs + o] = sum_i x[t, x_off + h * x_hs + i] * w[h, o, i]`` for every head h: one small
+    product per head.  w [H, n_out, n_in]; x float32 or bfloat16, w and y of one type (float32 sums in a fixed order)."""
+    _dev(x, "x", contiguous=False); _dev(w, "w"); _dev(y, "y", contiguous=False)
+    H, n_out, n_in = w.shape
+    T = x.shape[0]
+    if (x.dim() != 2 or y.dim() != 2 or y.shape[0] != T or x.stride(1) != 1 or y.stride(1) != 1
+            or x_off + (H - 1) * x_hs + n_in > x.shape[1] or y_off + (H - 1) * y_hs + n_out > y.shape[1]):
+        raise KernelError("headwise_linear: x [T, >= x_off + (H - 1) x_hs + n_in], y [T, >= y_off + (H - 1) y_hs + n_out]")
+    fn = _fn("latent", "bw_headwise_linear", [c_void_p, c_int, c_ll, c_int, c_void_p, c_int, c_void_p, c_int, c_ll, c_int,
+                                              c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(c_void_p(x.data_ptr() + x_off * x.element_size()), _code(x, "x"), x.stride(0), int(x_hs), _ptr(w), _code(w, "w"),
+              c_void_p(y.data_ptr() + y_off * y.element_size()), _code(y, "y"), y.stride(0), int(y_hs), T, H, n_in, n_out,
+              _stream()), "headwise_linear")
+    return y
 
 
 # ------------------------------------------------------------------ several copies of the stream (hyper-connections)

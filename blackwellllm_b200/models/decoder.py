@@ -5,7 +5,11 @@ them the configuration's optional constants (embedding multiplier, logit scale,
 logit soft cap), an optional vector of the position added to the embedding, and an
 optional stream that is kept as several copies (``ModelConfig.streams``: every block
 is then a "hyper" block, the stream is [T, streams * hidden], and the model's last
-norm reads the sum of the copies).
+norm reads the sum of the copies), an optional second embedding table addressed by a hash
+of the previous token and the token (``ModelConfig.bigram_embedding``; the previous token
+of a request is kept in a state slot of the model's own), and an optional mixing of the
+stream with the embedding's output before every pass over a repeated stretch of layers
+(``ModelConfig.pass_input``).
 
 It is driven by :class:`ModelConfig` alone and knows no architecture by name.
 Reference for the sequence of operations: src/core/engine.cpp:921-1041.
@@ -18,7 +22,7 @@ import torch
 
 from ..config.specs import ModelConfig
 from ..kernels import ops
-from ..parts import BuildContext, ParamSpec, build_block, build_norm
+from ..parts import BuildContext, FixedStateRequest, ParamSpec, build_block, build_norm
 from ..parts.block import flush_hyper_write
 from ..parts.linear import Linear
 
@@ -45,10 +49,19 @@ class DecoderModel:
                     raise ValueError(f"schedule entry {pos}: cache_of must name an earlier entry that owns its cache")
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
-        self._keeps_embedding = any(e.add_embedding for e in config.schedule)
+        self.bigram = config.bigram_embedding
+        self.bigram_table: Optional[torch.Tensor] = None
+        self.pass_input = config.pass_input
+        self.pass_in: List[Linear] = []        # one per pass: the same weight, the pass's own step vector as bias
+        opens = [e.pass_input for e in config.schedule if e.pass_input is not None]
+        if opens and self.pass_input is None:
+            raise ValueError("a schedule entry opens a pass but the model has no pass_input")
+        if self.pass_input is not None and any(not 0 <= t < self.pass_input.times for t in opens):
+            raise ValueError(f"a schedule entry opens a pass outside 0 .. {self.pass_input.times - 1}")
+        self._keeps_embedding = any(e.add_embedding for e in config.schedule) or bool(opens)
         self.streams = config.streams          # None: one plain stream
         if self.streams is not None:
-            if any(ls.block != "hyper" for ls in config.layers) or self._keeps_embedding:
+            if any(ls.block != "hyper" for ls in config.layers) or self._keeps_embedding or self.bigram is not None:
                 raise ValueError("a stream kept as several copies needs 'hyper' blocks throughout and no repeated stretch")
             if not hasattr(self.final_norm, "gain_f32"):
                 raise ValueError(f"{type(self.final_norm).__name__} cannot close a stream of several copies (it has no gain_f32)")
@@ -70,6 +83,12 @@ class DecoderModel:
         c = self.config
         specs: Dict[str, ParamSpec] = {}
         specs[c.embed_name] = ParamSpec(c.embed_name, (c.vocab_size, c.hidden_size))
+        if self.bigram is not None:
+            specs[self.bigram.name] = ParamSpec(self.bigram.name, (self.bigram.buckets + 1, c.hidden_size))
+        if self.pass_input is not None:
+            pi = self.pass_input
+            specs[pi.weight] = ParamSpec(pi.weight, (c.hidden_size, 2 * c.hidden_size))
+            specs[pi.step] = ParamSpec(pi.step, (pi.times, c.hidden_size), role="bias", init="bias_normal")
         for i, blk in enumerate(self.blocks):
             prefix = c.layer_prefix.format(i=i)
             for p in blk.param_specs():
@@ -85,6 +104,11 @@ class DecoderModel:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         c = self.config
         self.embed = tensors[c.embed_name].contiguous()
+        if self.bigram is not None:
+            self.bigram_table = tensors[self.bigram.name].to(self.embed.dtype).contiguous()
+        if self.pass_input is not None:
+            w, step = tensors[self.pass_input.weight], tensors[self.pass_input.step].float()
+            self.pass_in = [Linear(w, step[t].contiguous()) for t in range(self.pass_input.times)]
         for i, blk in enumerate(self.blocks):
             prefix = c.layer_prefix.format(i=i)
             blk.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
@@ -94,10 +118,14 @@ class DecoderModel:
 
     # ------------------------------------------------------------ caches
     def cache_requests(self) -> List[object]:
-        """Per schedule entry: what cache that run owns (None if it owns none)."""
+        """Per schedule entry: what cache that run owns (None if it owns none; a tuple if the block keeps something
+        beside its mixer's).  A model that keeps something per request itself (the previous token, for the hashed second
+        embedding table) asks for it in one more entry behind the schedule's."""
         out = []
         for e in self.config.schedule:
-            out.append(None if e.cache_of is not None else self.blocks[e.layer].mixer.cache_request())
+            out.append(None if e.cache_of is not None else self.blocks[e.layer].cache_request())
+        if self.bigram is not None:
+            out.append(FixedStateRequest((1,), torch.int32))
         return out
 
     # ------------------------------------------------------------ forward
@@ -110,16 +138,23 @@ class DecoderModel:
         if S is not None or self._pos_freq is not None:
             h = ops.embed_positions(self.embed, batch.token_ids, batch.positions, self._pos_freq, copies=S or 1,
                                     scale=c.embedding_multiplier)
+        elif self.bigram is not None:
+            b = self.bigram
+            h = ops.embed_bigram(self.embed, self.bigram_table, batch, caches[len(c.schedule)].state, b.buckets, b.mul_prev,
+                                 b.mul_cur, scale=c.embedding_multiplier)
         else:
             h = ops.embed_gather(self.embed, batch.token_ids, scale=c.embedding_multiplier)
         h0 = h.clone() if self._keeps_embedding else None   # the embedding's output, for repeated passes
         for pos, e in enumerate(self.config.schedule):
             cache = caches[e.cache_of if e.cache_of is not None else pos]
             blk = self.blocks[e.layer]
-            if not blk.takes_pending or e.add_embedding:
+            if not blk.takes_pending or e.add_embedding or e.pass_input is not None:
                 ops.resolve_pending()   # the block before may have left its last sum to the next reader
             if e.add_embedding:
                 ops.add_into(h, h0)
+            if e.pass_input is not None:
+                # the stream becomes W [x; x0] + step[t]: both streams side by side in the compute type, one product
+                self.pass_in[e.pass_input](ops.concat2_cast(h, h0, self.ctx.dtype), out=h)
             blk.forward(h, batch, cache, owns_cache=e.cache_of is None)
             if self.stream_hook is not None:
                 ops.resolve_pending()

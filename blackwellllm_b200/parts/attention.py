@@ -26,6 +26,12 @@ outputs times sigmoid(W_g x) before the output projection; W_g's rows ride in th
 attention kernels apply the sigmoid as they write a row), and
 ``shares_kv`` (no key and value tensors: the run reads the cache of the schedule entry it names, which the
 other layer filled earlier in the same step, with its own queries).
+
+And: ``gate_per_head`` (the output gate has one number per head), ``v_norm_eps`` (every value head divided by its
+root mean square, without a gain, before it is cached: done by the kernel that appends), ``distance_bias`` (two
+learned numbers per query head, r1 and r2: r1 ln(1 + r2 (i - j)) is taken off the score of query i and key j inside
+the attention kernels) and ``keep_first`` (with a window, the first so many keys of a sequence stay visible, and
+their pages stay with the request).
 """
 from __future__ import annotations
 
@@ -40,7 +46,8 @@ from .linear import Linear
 
 _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                   "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-                  "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks", "g": "g_proj.weight"}
+                  "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks", "g": "g_proj.weight",
+                  "r1": "r1", "r2": "r2"}
 
 
 class GQAAttention(Mixer):
@@ -64,15 +71,28 @@ class GQAAttention(Mixer):
         self.has_sink = bool(getattr(spec, "sink", False))
         self.gated = bool(getattr(spec, "output_gate", False))
         self.shares_kv = bool(getattr(spec, "shares_kv", False))
+        self.gate_per_head = bool(getattr(spec, "gate_per_head", False))
+        self.v_eps = getattr(spec, "v_norm_eps", None)
+        self.has_dist = bool(getattr(spec, "distance_bias", False))
+        self.keep_first = int(getattr(spec, "keep_first", 0) or 0)
+        if self.keep_first < 0:
+            raise ValueError("keep_first must not be negative")
+        if self.gate_per_head and not self.gated:
+            raise ValueError("gate_per_head goes with output_gate")
+        if self.v_eps is not None and self.shares_kv:
+            raise ValueError("a mixer that shares another run's keys and values norms no values")
+        self.dist = None
         self.names = dict(_DEFAULT_NAMES)
         self.names.update(dict(getattr(spec, "names", ()) or ()))
         # head size of the cache and the attention kernels: both sizes fit, in steps the kernels take
         step = 16 if ctx.dtype == torch.bfloat16 else 1
         self.dpad = -(-max(self.hd, self.dv) // step) * step
         self.general = (self.qk_norm_eps is not None or self.dv != self.hd or self.dpad != self.hd or self.norm_per_head
-                        or self.q_temp is not None or self.gated or self.shares_kv)
-        # the kernel that norms per head also takes rows with a gate's columns behind q, k, v, or without k and v
-        self.per_head_route = self.norm_per_head or self.q_temp is not None or self.shares_kv
+                        or self.q_temp is not None or self.gated or self.shares_kv or self.v_eps is not None)
+        # the kernel that norms per head also takes rows with a gate's columns behind q, k, v, or without k and v,
+        # and norms the values
+        self.per_head_route = (self.norm_per_head or self.q_temp is not None or self.shares_kv
+                               or self.v_eps is not None or self.gate_per_head)
         if self.shares_kv and self.qkv_bias:
             raise ValueError("a mixer that shares another run's keys and values has no key and value biases")
         if self.per_head_route and self.qk_norm_eps is not None and not self.norm_per_head:
@@ -90,7 +110,7 @@ class GQAAttention(Mixer):
 
     def cache_request(self):
         # (a run with ``shares_kv`` is never asked: its schedule entry names the run whose cache it reads)
-        return PagedKVRequest(self.nkv, self.dpad, self.window)
+        return PagedKVRequest(self.nkv, self.dpad, self.window, self.keep_first if self.window else 0)
 
     def param_specs(self) -> List[ParamSpec]:
         H, q, k, v = self.hidden_size, self.nh * self.hd, self.nkv * self.hd, self.nkv * self.dv
@@ -110,7 +130,10 @@ class GQAAttention(Mixer):
         if self.has_sink:
             specs.append(ParamSpec(n["sink"], (self.nh,), role="bias", init="bias_normal"))
         if self.gated:
-            specs.append(ParamSpec(n["g"], (self.nh * self.dv, H)))
+            specs.append(ParamSpec(n["g"], (self.nh if self.gate_per_head else self.nh * self.dv, H)))
+        if self.has_dist:
+            specs += [ParamSpec(n["r1"], (self.nh,), role="bias", init="bias_normal"),
+                      ParamSpec(n["r2"], (self.nh,), role="bias", init="ones")]
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -118,6 +141,8 @@ class GQAAttention(Mixer):
         parts = [tensors[n["q"]]] + ([] if self.shares_kv else [tensors[n["k"]], tensors[n["v"]]])
         if self.has_sink:
             self.sink = tensors[n["sink"]].float().contiguous()
+        if self.has_dist:
+            self.dist = torch.stack([tensors[n["r1"]].float(), tensors[n["r2"]].float()]).contiguous()
         if self.gated:
             if self.per_head_route or self.qk_norm_eps is None:
                 # the gate's rows ride in the q/k/v product; the kernel that follows leaves its columns alone
@@ -156,7 +181,8 @@ class GQAAttention(Mixer):
             if self.per_head_route or (self.gated and self.gate is None):
                 q = self.position.norm_rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, self.dv, self.q_gain,
                                                      self.k_gain, float(self.qk_norm_eps or 0.0), append=owns_cache,
-                                                     per_head=True, q_temp=self.q_temp, has_kv=not self.shares_kv)
+                                                     per_head=True, q_temp=self.q_temp, has_kv=not self.shares_kv,
+                                                     v_eps=float(self.v_eps or 0.0))
             elif self.general:
                 q = self.position.norm_rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, self.dv, self.q_gain,
                                                      self.k_gain, float(self.qk_norm_eps or 0.0), append=owns_cache)
@@ -164,11 +190,15 @@ class GQAAttention(Mixer):
                 q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)
         gate = None
         if self.gated:   # the attention kernels multiply by the gate's sigmoid as they write a row
-            g = self.gate(x, out_dtype=torch.float32) if self.gate is not None \
-                else qkv[:, self.g_off:self.g_off + self.nh * self.dv]
-            gate = (g, self.dv)
+            if self.gate_per_head:
+                gate = (qkv[:, self.g_off:self.g_off + self.nh], self.dv, "head")
+            else:
+                g = self.gate(x, out_dtype=torch.float32) if self.gate is not None \
+                    else qkv[:, self.g_off:self.g_off + self.nh * self.dv]
+                gate = (g, self.dv)
         o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group],
-                                self.nh, self.window, self.scale, self.chunk, self.sink, gate)
+                                self.nh, self.window, self.scale, self.chunk, self.sink, gate, self.dist,
+                                self.keep_first if self.window else 0)
         if accumulate:
             self.o.add_to(o, residual)
         elif accumulate is None:

@@ -63,10 +63,14 @@ class BuildContext:
 @dataclass(frozen=True)
 class PagedKVRequest:
     """A mixer's need for paged keys and values: per token ``2 * num_kv_heads *
-    head_dim`` elements; ``window``: only that many latest tokens stay needed."""
+    head_dim`` elements; ``window``: only that many latest tokens stay needed, and with ``keep_first`` the
+    first so many tokens of a request as well.  ``single_plane``: keys and values are the same rows (a mixer
+    whose values are a part of its key rows): one plane is kept and both views show it."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
+    single_plane: bool = False
 
 
 @dataclass(frozen=True)
@@ -74,6 +78,16 @@ class FixedStateRequest:
     """A mixer's need for a state of fixed size per request (zeroed at admission)."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+def flatten_cache_requests(request) -> tuple:
+    """A run's cache request as a tuple of single needs: a run may ask for several things at once (pages for its
+    mixer and a state for the block around it) by returning a tuple; None: nothing."""
+    if request is None:
+        return ()
+    if isinstance(request, (tuple, list)):
+        return tuple(r for r in request if r is not None)
+    return (request,)
 
 
 class Part:
@@ -101,13 +115,15 @@ class PositionEncoding(Part):
         raise NotImplementedError
 
     def norm_rotate_append(self, qkv, batch, cache, nh: int, nkv: int, dq: int, dv: int, q_gain, k_gain, eps: float,
-                           append: bool = True, per_head: bool = False, q_temp=None, has_kv: bool = True) -> torch.Tensor:
+                           append: bool = True, per_head: bool = False, q_temp=None, has_kv: bool = True,
+                           v_eps: float = 0.0) -> torch.Tensor:
         """The general form of :meth:`rotate_append`: qkv [T, nh*dq + nkv*dq + nkv*dv] float32; with gains,
         all query channels of a token (and all its key channels) are RMS-normed together first; the cache's
         head size may exceed dq and dv (the rest is written as zeros).  ``per_head``: every head is normed by
         itself (gains of dq entries, shared by the heads) and qkv may have further columns, which are left
         alone; ``q_temp`` (coef, every): the queries are multiplied by 1 + coef log(1 + n), n the whole periods of ``every`` positions in p + 1;
-        ``has_kv=False``: qkv holds queries only and nothing is appended."""
+        ``has_kv=False``: qkv holds queries only and nothing is appended; ``v_eps`` > 0: every value head is divided
+        by sqrt(mean(v^2) + v_eps) before it is written."""
         raise NotImplementedError
 
     def fuse_projection(self, weight: torch.Tensor, bias: Optional[torch.Tensor], nh: int, nkv: int, hd: int):
@@ -138,6 +154,11 @@ class Block(Part):
     # True: forward() may be entered, and may return, with a sum outstanding for the residual stream
     # (ops.gemm_tc_deferred) and sees to it that no part reads the stream before the sum is made.
     takes_pending = False
+
+    def cache_request(self):
+        """What a run of this block owns in the cache manager: the mixer's need, or a tuple of needs when the block
+        keeps something of its own per request (the run's cache view is then a tuple in the same order)."""
+        return self.mixer.cache_request()
 
     def forward(self, residual, batch, cache, owns_cache: bool = True) -> None:
         raise NotImplementedError

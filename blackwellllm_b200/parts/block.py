@@ -185,3 +185,71 @@ def flush_hyper_write(residual, batch, streams: int) -> None:
 
 
 register_block("hyper", HyperBlock)
+
+
+class ParallelBlock(PreNormBlock):
+    """ONE norm whose output both sublayers read: ``h = norm(x)``, ``x += mixer(h') + ffn(h)``.  With the layer's
+    ``token_shift`` (a vector s), the mixer reads ``h'_t = h_t + (h_{t-1} - h_t) * s`` (zeros before a sequence's first
+    token) and the feed-forward h_t as it is; norm and shift are one kernel, and h of a request's last token is kept in a
+    state slot of the block's own between steps (every run of the block has its own)."""
+    takes_pending = False
+
+    def __init__(self, layer_spec, hidden_size: int, ctx: BuildContext):
+        self.spec = layer_spec
+        self.mixer_norm = build_norm(layer_spec.mixer_norm, hidden_size, ctx)
+        self.mixer = build_mixer(layer_spec.mixer, hidden_size, ctx)
+        self.ffn = build_ffn(layer_spec.ffn, hidden_size, ctx) if layer_spec.ffn is not None else None
+        self.ffn_norm = None                   # there is one norm
+        if layer_spec.ffn_norm is not None:
+            raise ValueError("the parallel arrangement has one norm (mixer_norm); ffn_norm must be None")
+        self.hidden_size = hidden_size
+        self.ctx = ctx
+        self.shift_name = getattr(layer_spec, "token_shift", None)
+        self.shift = None
+        if self.shift_name is not None and not hasattr(self.mixer_norm, "gain_f32"):
+            raise ValueError(f"{type(self.mixer_norm).__name__} cannot stand before a token shift (it has no gain_f32)")
+
+    def _children(self):
+        s = self.spec
+        kids = [(s.mixer_norm_prefix, self.mixer_norm), (s.mixer_prefix, self.mixer)]
+        if self.ffn is not None:
+            kids.append((s.ffn_prefix, self.ffn))
+        return kids
+
+    def param_specs(self) -> List[ParamSpec]:
+        out = super().param_specs()
+        if self.shift_name is not None:
+            out.append(ParamSpec(self.shift_name, (self.hidden_size,), role="bias", init="bias_normal"))
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        super().bind(tensors)
+        if self.shift_name is not None:
+            self.shift = tensors[self.shift_name].float().contiguous()
+
+    def cache_request(self):
+        rq = self.mixer.cache_request()
+        if self.shift_name is None:
+            return rq
+        # the mixer's need first (None stays in its place), then the previous token's normed row
+        from .base import FixedStateRequest
+        return (rq, FixedStateRequest((self.hidden_size,), torch.float32)) if rq is not None \
+            else (FixedStateRequest((self.hidden_size,), torch.float32),)
+
+    def forward(self, residual, batch, cache, owns_cache: bool = True) -> None:
+        ops.resolve_pending()
+        if self.shift_name is not None:
+            if not owns_cache:
+                raise ops.KernelError("a block with a token shift owns its state: it cannot run on another run's cache")
+            mixer_cache, state = (cache[0], cache[1]) if len(cache) == 2 else (None, cache[0])
+            h, hs = ops.rmsnorm_shift(residual, self.mixer_norm.gain_f32(), self.shift, state.state, batch,
+                                      self.mixer_norm.eps, self.ctx.dtype, want_h=self.ffn is not None)
+        else:
+            mixer_cache = cache
+            h = hs = self.mixer_norm.forward(residual)
+        self.mixer.forward(hs, residual, batch, mixer_cache, owns_cache)
+        if self.ffn is not None:
+            self.ffn.forward(h, residual, batch)
+
+
+register_block("parallel", ParallelBlock)

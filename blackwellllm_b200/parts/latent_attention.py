@@ -1,0 +1,101 @@
+"""Latent attention: the keys and values of all heads are made from one small vector per token.
+
+    q_h = W_q,h x                      laid out per head as [head_dim plain channels, rot_dim rotated channels]
+    [c_raw, k_rot] = W_dkv x           kv_rank + rot_dim rows;  c = c_raw / rms(c_raw) * gain  (the latent)
+    k_h = [W_uk,h c, rot(k_rot)]       v_h = W_uv,h c
+    score_h(i, j) = (q_plain,h(i) . W_uk,h c(j) + rot(q_rot,h(i)) . rot(k_rot(j))) * scale
+    y = W_o concat_h(sum_j p_h(i, j) v_h(j))          p: softmax over the window, with an optional sink per head
+
+Only c and the rotated k_rot are cached: one row of kv_rank + rot_dim channels per token, shared by all heads.  The
+heads' matrices are moved to the other side of the two sums ("absorbed"):
+
+    q_plain,h . (W_uk,h c) = (W_uk,h^T q_plain,h) . c            sum_j p v_h(j) = W_uv,h (sum_j p c(j))
+
+so the attention proper is a grouped-query attention with ONE key/value head whose key row is [c, k_rot] and whose
+value row is c, a part of the same row: the framework's paged attention kernels run it as they are (sink, window), on a
+cache with a single plane (``PagedKVRequest.single_plane``).  Around them: one product for q and the latent's
+projection (float32 results); ``ops.latent_prep`` (norm of the latent, rotation of the shared key part and the queries'
+rotated parts, append); ``ops.headwise_linear`` with W_uk,h^T on the queries' plain parts and with W_uv,h on the
+attention's output; the output projection into the stream.  The rotation is the rotary encoding part's own table
+(YaRN frequencies and magnitude included); the norm, the angles, the scores and the softmax are float32.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..kernels import ops
+from .base import BuildContext, Mixer, PagedKVRequest, ParamSpec, build_position, register_mixer
+from .linear import Linear
+
+_DEFAULT_NAMES = {"q": "q_proj.weight", "dkv": "kv_a_proj.weight", "dkv_norm": "kv_a_norm.weight", "uk": "k_b_proj.weight",
+                  "uv": "v_b_proj.weight", "o": "o_proj.weight", "sink": "sinks"}
+
+
+class LatentAttention(Mixer):
+    def __init__(self, spec, hidden_size: int, ctx: BuildContext):
+        self.H, self.d, self.dr = int(spec.num_heads), int(spec.head_dim), int(spec.rot_dim)
+        self.dv, self.rank = int(spec.v_head_dim), int(spec.kv_rank)
+        self.eps = float(spec.norm_eps)
+        self.scale = float(spec.softmax_scale)
+        self.window = spec.window
+        self.has_sink = bool(spec.sink)
+        self.hidden_size = hidden_size
+        self.ctx = ctx
+        self.names = dict(_DEFAULT_NAMES)
+        self.names.update(dict(getattr(spec, "names", ()) or ()))
+        if self.dr <= 0 or self.dr % 2:
+            raise ValueError(f"rot_dim {self.dr} must be even and positive")
+        step = 16 if ctx.dtype == torch.bfloat16 else 1
+        self.dpad = -(-(self.rank + self.dr) // step) * step      # the cached row, in steps the attention kernels take
+        ops.check_attention_supported(ctx.dtype, self.dpad, self.H)   # all heads share the one key/value head
+        self.position = build_position(spec.position, self.dr, ctx)
+        if getattr(self.position, "rotary_dim", None) != self.dr or getattr(self.position, "interleaved", False):
+            raise ValueError("latent attention turns all rot_dim channels, channel i with channel i + rot_dim / 2")
+        self.proj: Linear = None
+        self.uk_t = self.uv = self.c_gain = self.sink = None
+        self.o: Linear = None
+
+    def cache_request(self):
+        return PagedKVRequest(1, self.dpad, self.window, 0, single_plane=True)
+
+    def param_specs(self) -> List[ParamSpec]:
+        W, n = self.hidden_size, self.names
+        specs = [ParamSpec(n["q"], (self.H * (self.d + self.dr), W)), ParamSpec(n["dkv"], (self.rank + self.dr, W)),
+                 ParamSpec(n["dkv_norm"], (self.rank,), role="gain", init="ones"),
+                 ParamSpec(n["uk"], (self.H * self.d, self.rank)), ParamSpec(n["uv"], (self.H * self.dv, self.rank)),
+                 ParamSpec(n["o"], (W, self.H * self.dv))]
+        if self.has_sink:
+            specs.append(ParamSpec(n["sink"], (self.H,), role="bias", init="bias_normal"))
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.proj = Linear(torch.cat([tensors[n["q"]], tensors[n["dkv"]]], dim=0))
+        self.c_gain = tensors[n["dkv_norm"]].float().contiguous()
+        # per head [outputs, inputs]: W_uk,h^T takes head_dim inputs to kv_rank outputs, W_uv,h kv_rank inputs to v_head_dim
+        self.uk_t = tensors[n["uk"]].view(self.H, self.d, self.rank).transpose(1, 2).contiguous()
+        self.uv = tensors[n["uv"]].view(self.H, self.dv, self.rank).contiguous()
+        self.o = Linear(tensors[n["o"]])
+        self.sink = tensors[n["sink"]].float().contiguous() if self.has_sink else None
+
+    def forward(self, x, residual, batch, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
+        H, d, dr, rank = self.H, self.d, self.dr, self.rank
+        proj = self.proj(x, out_dtype=torch.float32)       # [T, H * (d + dr) | rank + dr]
+        q = ops.latent_prep(proj, 0, H * (d + dr), batch, batch.block_tables[cache.group], self.position.table(batch),
+                            self.c_gain, self.eps, cache.k_pages, H, d, dr, rank, append=owns_cache)
+        ops.headwise_linear(proj, 0, d + dr, self.uk_t, q, 0, self.dpad)
+        o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group], H, self.window,
+                                self.scale, None, self.sink, None)
+        y = torch.empty((x.shape[0], H * self.dv), dtype=x.dtype, device=x.device)
+        ops.headwise_linear(o, 0, self.dpad, self.uv, y, 0, self.dv)
+        if accumulate:
+            self.o.add_to(y, residual)
+        elif accumulate is None:
+            self.o.write_to(y, residual)
+        else:
+            self.o(y, out=residual)
+
+
+register_mixer("latent_attention", LatentAttention)

@@ -39,25 +39,37 @@ class SwiGLU(FeedForward):
         self.limit, self.alpha = float(getattr(spec, "act_limit", 0.0)), float(getattr(spec, "act_alpha", 1.0))
         self.gate_name, self.up_name, self.down_name = getattr(spec, "names", None) or (
             "gate_proj.weight", "up_proj.weight", "down_proj.weight")
+        self.bias_names = getattr(spec, "bias_names", None)
 
     def param_specs(self) -> List[ParamSpec]:
         I, H = self.intermediate_size, self.hidden_size
-        return [ParamSpec(self.gate_name, (I, H)), ParamSpec(self.up_name, (I, H)), ParamSpec(self.down_name, (H, I))]
+        specs = [ParamSpec(self.gate_name, (I, H)), ParamSpec(self.up_name, (I, H)), ParamSpec(self.down_name, (H, I))]
+        if self.bias_names is not None:
+            specs += [ParamSpec(n, (size,), role="bias", init="bias_normal") for n, size in zip(self.bias_names, (I, I, H))]
+        return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors[self.gate_name], tensors[self.up_name]
-        self.fused = (g.dtype == torch.bfloat16 and g.is_cuda
-                      and self.intermediate_size % ops.SWIGLU_BLOCK == 0 and self.hidden_size % 8 == 0)
+        bias = down_bias = None
+        if self.bias_names is not None:
+            bg, bu, down_bias = (tensors[n] for n in self.bias_names)
+            dt = bg.dtype if bg.dtype == bu.dtype else torch.float32
+            bias = (bg.to(dt), bu.to(dt))
+        self.fused = (g.dtype == torch.bfloat16 and g.is_cuda and self.act in ops.GEMM_TC_GATED_ACTIVATIONS
+                      and (bias is None or ops.GEMM_TC_GATED_BIAS) and self.intermediate_size % ops.SWIGLU_BLOCK == 0 and self.hidden_size % 8 == 0)
         if self.fused:
-            self.gate_up = Linear(ops.interleave_gate_up(g, u))
+            # the bias of the interleaved rows is interleaved the same way
+            b = None if bias is None else ops.interleave_gate_up(bias[0].view(-1, 1), bias[1].view(-1, 1)).view(-1)
+            self.gate_up = Linear(ops.interleave_gate_up(g, u), b)
         else:
-            self.gate_up = Linear(torch.cat([g, u], dim=0))
-        self.down = Linear(tensors[self.down_name])
+            self.gate_up = Linear(torch.cat([g, u], dim=0), None if bias is None else torch.cat(bias))
+        self.down = Linear(tensors[self.down_name], down_bias)
 
     def forward(self, x, residual, batch, accumulate: bool = True) -> None:
         if self.fused:
-            a = ops.gemm_tc(x, self.gate_up.weight, swiglu=True, act=self.act, limit=self.limit, alpha=self.alpha)
-        elif self.act == ops.ACT_SILU:
+            a = ops.gemm_tc(x, self.gate_up.weight, self.gate_up.bias, swiglu=True, act=self.act, limit=self.limit,
+                            alpha=self.alpha)
+        elif self.act == ops.ACT_SILU and self.gate_up.bias is None:
             a = ops.swiglu(self.gate_up(x))
         else:
             a = ops.glu(self.gate_up(x, out_dtype=torch.float32), self.act, self.limit, self.alpha, out_dtype=x.dtype)

@@ -79,12 +79,16 @@ class RotaryEncoding(PositionEncoding):
             batch.extras[self._key] = table
         return table
 
+    def table(self, batch):
+        """float32 [T, rotary_dim]: the cosines, then the sines of the step's positions (times the magnitude)."""
+        return self._table(batch)
+
     def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True,
-                           per_head=False, q_temp=None, has_kv=True):
-        if per_head or q_temp is not None or not has_kv:
+                           per_head=False, q_temp=None, has_kv=True, v_eps=0.0):
+        if per_head or q_temp is not None or not has_kv or v_eps:
             return ops.head_norm_rope_append(qkv, batch, batch.block_tables[cache.group], self._table(batch), self.rotary_dim,
                                              self.interleaved, q_gain, k_gain, eps, cache.k_pages, cache.v_pages, nh, nkv,
-                                             dq, dv, has_kv=has_kv, append=append, q_temp=q_temp)
+                                             dq, dv, has_kv=has_kv, append=append, q_temp=q_temp, v_eps=v_eps)
         return ops.qk_norm_rope_append(qkv, batch, batch.block_tables[cache.group], self._table(batch), self.rotary_dim,
                                        self.interleaved, q_gain, k_gain, eps, cache.k_pages, cache.v_pages, nh, nkv,
                                        dq, dv, append=append)
@@ -147,11 +151,11 @@ class NoPosition(PositionEncoding):
                                None, 0, cache.k_pages, cache.v_pages, nh, nkv, hd, append=append)
 
     def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True,
-                           per_head=False, q_temp=None, has_kv=True):
-        if per_head or q_temp is not None or not has_kv:
+                           per_head=False, q_temp=None, has_kv=True, v_eps=0.0):
+        if per_head or q_temp is not None or not has_kv or v_eps:
             return ops.head_norm_rope_append(qkv, batch, batch.block_tables[cache.group], None, 0, False, q_gain, k_gain,
                                              eps, cache.k_pages, cache.v_pages, nh, nkv, dq, dv, has_kv=has_kv,
-                                             append=append, q_temp=q_temp)
+                                             append=append, q_temp=q_temp, v_eps=v_eps)
         return ops.qk_norm_rope_append(qkv, batch, batch.block_tables[cache.group], None, 0, False, q_gain, k_gain,
                                        eps, cache.k_pages, cache.v_pages, nh, nkv, dq, dv, append=append)
 
