@@ -46,6 +46,11 @@ struct Params {
     // sink != null: a row's softmax has one more term exp(sink[query head]) that has no key and no value
     // (its weight goes nowhere: the row's weights sum to less than one); float32 [nh], not scaled.
     const float* sink;
+    // dist != null: float32 [2][nh] (r1 of every query head, then r2): r1 ln(1 + r2 (i - j)) is taken off the score of
+    // query position i and key position j.  keep_first: the first so many keys of a sequence stay visible beyond
+    // the window (0: none).
+    const float* dist;
+    int keep_first;
     // gate != null: every output channel c < gate_dv of (token, head) is multiplied by sigmoid(gate[token * gate_ld +
     // head * gate_dv + c]) as it is written, channels from gate_dv on become zero (bw::out_gate)
     const float* gate; long long gate_ld; int gate_dv;
@@ -147,7 +152,63 @@ __device__ __forceinline__ void load_q_rows(const Params& p, int tok_base, int g
 struct RowState {
     float m[2], l[2];      // rows lane/4 and lane/4 + 8 of the warp's 16
     int qpos[2], lo[2];    // the rows' own positions and first visible key (qpos < 0: no such row)
+    float r1[2], r2[2];    // the rows' heads' distance bias (used when dist != 0)
+    int keep, dist;        // keys below `keep` stay visible; dist != 0: the launch has a distance bias
 };
+
+// The tiles a query tile walks when first keys are kept: the tiles that hold kept keys and lie before the first
+// tile of the window (`kept` of them), then the tiles from t_first on.  v counts along that walk.
+__device__ __forceinline__ int kept_tiles(int keep_first, int t_first) {
+    const int n = (keep_first + BN - 1) / BN;
+    return keep_first > 0 ? (n < t_first ? n : t_first) : 0;
+}
+__device__ __forceinline__ int walk_tile(int v, int kept, int t_first) { return v < kept ? v : t_first + (v - kept); }
+
+// Scores of one slab in powers of two: scaled, the distance bias taken off, keys that a row does not see at
+// -infinity; mx: the rows' maxima.  key_pos0: the position of the slab's first key.
+template <int NK>
+__device__ __forceinline__ void scale_and_mask(float (&s)[NK / 8][4], int key_pos0, bool need_mask, float scale_log2,
+                                               const RowState& st, float (&mx)[2]) {
+    const int lane = threadIdx.x & 31;
+    if (st.dist) {   // (uniform over the launch) r1 ln(1 + r2 d) log2(e) = r1 log2(1 + r2 d)
+#pragma unroll
+        for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int kp = key_pos0 + j * 8 + 2 * (lane & 3) + (e & 1);
+                const int d = st.qpos[h] - kp;
+                const bool seen = d >= 0 && (kp >= st.lo[h] || kp < st.keep);
+                const float b = st.r1[h] * __log2f(fmaf(st.r2[h], (float)(d > 0 ? d : 0), 1.f));
+                const float v = seen ? fmaf(s[j][e], scale_log2, -b) : -INFINITY;
+                s[j][e] = v;
+                mx[h] = fmaxf(mx[h], v);
+            }
+        }
+    } else if (need_mask) {   // one branch per tile, not one per score
+#pragma unroll
+        for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int kp = key_pos0 + j * 8 + 2 * (lane & 3) + (e & 1);
+                const float v = (kp > st.qpos[h] || (kp < st.lo[h] && kp >= st.keep)) ? -INFINITY : s[j][e] * scale_log2;
+                s[j][e] = v;
+                mx[h] = fmaxf(mx[h], v);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = s[j][e] * scale_log2;
+                s[j][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+    }
+}
 
 // One slab of NK keys (starting k_off rows into the tiles) for the warp's 16 query rows.
 template <int NK>
@@ -169,31 +230,9 @@ __device__ __forceinline__ void process_keys(const uint32_t (&qf)[KSTEPS][4], co
             mma_bf16(s[2 * nb + 1], qf[ks], b2, b3);
         }
     }
-    // scale, mask, online softmax
+    // scale, bias, mask, online softmax
     float mx[2] = {-INFINITY, -INFINITY};
-    if (need_mask) {   // one branch per tile, not one per score
-#pragma unroll
-        for (int j = 0; j < NK / 8; ++j) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const int kp = key_pos0 + k_off + j * 8 + 2 * (lane & 3) + (e & 1);
-                const float v = (kp > st.qpos[h] || kp < st.lo[h]) ? -INFINITY : s[j][e] * scale_log2;
-                s[j][e] = v;
-                mx[h] = fmaxf(mx[h], v);
-            }
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < NK / 8; ++j) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float v = s[j][e] * scale_log2;
-                s[j][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
-        }
-    }
+    scale_and_mask<NK>(s, key_pos0 + k_off, need_mask, scale_log2, st, mx);
     float corr[2], mu[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -244,15 +283,18 @@ __device__ __forceinline__ void load_q_frags(const uint8_t* q_rows, uint32_t (&q
     for (int ks = 0; ks < KSTEPS; ++ks) ldsm_x4(base + ks * 32, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
 }
 
-__device__ __forceinline__ void init_rows(const Params& p, RowState& st, int row_base, int n_rows, int q_pos0) {
+__device__ __forceinline__ void init_rows(const Params& p, RowState& st, int row_base, int n_rows, int q_pos0, int g) {
     const int lane = threadIdx.x & 31;
+    st.keep = p.keep_first; st.dist = p.dist != nullptr;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int row = row_base + (lane >> 2) + 8 * h;
         st.m[h] = -INFINITY; st.l[h] = 0.f;
+        st.r1[h] = st.r2[h] = 0.f;
         if (row < n_rows) {
             st.qpos[h] = q_pos0 + row / p.G;
             st.lo[h] = bw::first_visible(st.qpos[h], p.window, p.chunk);
+            if (p.dist) { const int head = g * p.G + row % p.G; st.r1[h] = p.dist[head]; st.r2[h] = p.dist[p.nh + head]; }
         } else { st.qpos[h] = -1; st.lo[h] = 0; }
     }
 }
@@ -282,11 +324,13 @@ attn_rows_kernel(Params p, int toks_per_tile) {
     const int last_pos = q_pos0 + ntok - 1;
     const int first_key = bw::first_visible(q_pos0, p.window, p.chunk);
     const int t_lo = first_key / BN, t_hi = last_pos / BN;   // inclusive
-    load_kv_tile(p, bt, g, kv_len, t_lo * BN, kv, kv + TILE_BYTES);
+    const int kept = kept_tiles(p.keep_first, t_lo);         // tiles of kept first keys that lie before the window's
+    const int n_walk = kept + t_hi - t_lo + 1;
+    load_kv_tile(p, bt, g, kv_len, walk_tile(0, kept, t_lo) * BN, kv, kv + TILE_BYTES);
     cp_async_commit();
 
     RowState st;
-    init_rows(p, st, warp * 16, n_rows, q_pos0);
+    init_rows(p, st, warp * 16, n_rows, q_pos0, g);
     float o[HD / 8][4];
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
@@ -298,17 +342,18 @@ attn_rows_kernel(Params p, int toks_per_tile) {
     const bool warp_live = warp * 16 < n_rows;
     const int warp_last_pos = q_pos0 + min(n_rows - 1, warp * 16 + 15) / p.G;
 
-    for (int t = t_lo; t <= t_hi; ++t) {
-        const int stage = (t - t_lo) & 1;
+    for (int v = 0; v < n_walk; ++v) {
+        const int t = walk_tile(v, kept, t_lo);
+        const int stage = v & 1;
         uint8_t* k_tile = kv + stage * 2 * TILE_BYTES;
-        if (t < t_hi) load_kv_tile(p, bt, g, kv_len, (t + 1) * BN, kv + (stage ^ 1) * 2 * TILE_BYTES,
-                                   kv + (stage ^ 1) * 2 * TILE_BYTES + TILE_BYTES);
+        if (v + 1 < n_walk) load_kv_tile(p, bt, g, kv_len, walk_tile(v + 1, kept, t_lo) * BN, kv + (stage ^ 1) * 2 * TILE_BYTES,
+                                         kv + (stage ^ 1) * 2 * TILE_BYTES + TILE_BYTES);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
         if (warp_live && t * BN <= warp_last_pos) {
             const int warp_first_pos = q_pos0 + (warp * 16) / p.G;
-            const bool need_mask = (t * BN + BN - 1 > warp_first_pos) ||
+            const bool need_mask = v < kept || (t * BN + BN - 1 > warp_first_pos) ||
                                    (t * BN < bw::first_visible(warp_last_pos, p.window, p.chunk));
             process_keys<BN>(qf, k_tile, k_tile + TILE_BYTES, 0, t * BN, need_mask, p.scale_log2, st, o);
         }
@@ -411,35 +456,38 @@ attn_keys_kernel(Params p) {
     const int last_pos = q_pos0 + q_len - 1;
     const int first_key = bw::first_visible(q_pos0, p.window, p.chunk);
     const int t_first = first_key / BN, t_end = last_pos / BN + 1;
-    const int per = (t_end - t_first + n_slices - 1) / n_slices;
-    const int t_lo = t_first + slice * per, t_hi = min(t_end, t_lo + per) - 1;   // inclusive; may be empty
+    const int kept = kept_tiles(p.keep_first, t_first);      // tiles of kept first keys that lie before the window's
+    const int n_walk = kept + t_end - t_first;               // the slices share the walk (walk_tile)
+    const int per = (n_walk + n_slices - 1) / n_slices;
+    const int v_lo = slice * per, v_hi = min(n_walk, v_lo + per) - 1;   // inclusive; may be empty
 
     RowState st;
-    init_rows(p, st, 0, n_rows, q_pos0);
+    init_rows(p, st, 0, n_rows, q_pos0, g);
     float o[HD / 8][4];
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
 
-    if (t_lo <= t_hi) {
+    if (v_lo <= v_hi) {
         load_q_rows(p, p.cu_q[r], g, 0, n_rows, q_tile, 16);
         cp_async_commit();
-        load_kv_tile(p, bt, g, kv_len, t_lo * BN, kv, kv + TILE_BYTES);
+        load_kv_tile(p, bt, g, kv_len, walk_tile(v_lo, kept, t_first) * BN, kv, kv + TILE_BYTES);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
         uint32_t qf[KSTEPS][4];
         load_q_frags(q_tile, qf);
-        for (int t = t_lo; t <= t_hi; ++t) {
-            const int stage = (t - t_lo) & 1;
+        for (int v = v_lo; v <= v_hi; ++v) {
+            const int t = walk_tile(v, kept, t_first);
+            const int stage = (v - v_lo) & 1;
             uint8_t* k_tile = kv + stage * 2 * TILE_BYTES;
-            if (t < t_hi) load_kv_tile(p, bt, g, kv_len, (t + 1) * BN, kv + (stage ^ 1) * 2 * TILE_BYTES,
+            if (v < v_hi) load_kv_tile(p, bt, g, kv_len, walk_tile(v + 1, kept, t_first) * BN, kv + (stage ^ 1) * 2 * TILE_BYTES,
                                        kv + (stage ^ 1) * 2 * TILE_BYTES + TILE_BYTES);
             cp_async_commit();
             cp_async_wait<1>();
             __syncthreads();
             const int k_off = warp * 16;
             if (t * BN + k_off <= last_pos) {
-                const bool need_mask = (t * BN + BN - 1 > q_pos0) || (t * BN < bw::first_visible(last_pos, p.window, p.chunk));
+                const bool need_mask = v < kept || (t * BN + BN - 1 > q_pos0) || (t * BN < bw::first_visible(last_pos, p.window, p.chunk));
                 process_keys<16>(qf, k_tile, k_tile + TILE_BYTES, k_off, t * BN, need_mask, p.scale_log2, st, o);
             }
             __syncthreads();
@@ -483,29 +531,7 @@ __device__ __forceinline__ void process_keys_swz(const uint32_t (&qf)[KSTEPS][4]
         }
     }
     float mx[2] = {-INFINITY, -INFINITY};
-    if (need_mask) {   // one branch per tile, not one per score
-#pragma unroll
-        for (int j = 0; j < NK / 8; ++j) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const int kp = key_pos0 + k_off + j * 8 + 2 * (lane & 3) + (e & 1);
-                const float v = (kp > st.qpos[h] || kp < st.lo[h]) ? -INFINITY : s[j][e] * scale_log2;
-                s[j][e] = v;
-                mx[h] = fmaxf(mx[h], v);
-            }
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < NK / 8; ++j) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float v = s[j][e] * scale_log2;
-                s[j][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
-        }
-    }
+    scale_and_mask<NK>(s, key_pos0 + k_off, need_mask, scale_log2, st, mx);
     float corr[2], mu[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -695,7 +721,7 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     };
 
     RowState st;
-    init_rows(p, st, 0, n_rows, q_pos0);
+    init_rows(p, st, 0, n_rows, q_pos0, g);
     float o[HD / 8][4];
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
@@ -917,8 +943,9 @@ BW_EXPORT int bw_attention_head_dim() { return HD; }
 // the q/k/v product itself: float32 [qkv_planes][tokens][(nh + 2 nkv) * HD], the planes qkv_plane_stride
 // floats apart and added in order, the rotated channels of the q and k heads as (j, j + rd / 2) pairs;
 // rope_table float32 [tokens][rd] (cosines, then sines); append != 0: key and value also go to the cache.
-// sink: float32 [nh] or null; gate: float32 [tokens, >= nh * gate_dv] with rows gate_ld apart, or null (see Params).
-// Only where the TMA key-slice kernel runs (head size a multiple of 64, pages of 8 to 64 tokens);
+// sink: float32 [nh] or null; gate: float32 [tokens, >= nh * gate_dv] with rows gate_ld apart, or null (see Params);
+// gate_dv < 0: one gate number per head (bw::out_gate).  dist: float32 [2][nh] or null; keep_first: see Params.
+// qkv only where the TMA key-slice kernel runs (head size a multiple of 64, pages of 8 to 64 tokens);
 // BW_ERR_UNSUPPORTED otherwise, and nothing was launched.
 BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
                                const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
@@ -927,7 +954,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
                                int nkv, int page_size, int num_pages, int window, int chunk, float scale,
                                const float* qkv, int qkv_planes, long long qkv_plane_stride, const float* rope_table,
                                int rd, int append, int merge_max_slices, const float* sink, const float* gate, long long gate_ld,
-                               int gate_dv, void* stream) {
+                               int gate_dv, const float* dist, int keep_first, void* stream) {
     if (nkv <= 0 || nh % nkv != 0) return BW_ERR_BAD_ARG;
     const int G = nh / nkv;
     if (G > 16) return BW_ERR_UNSUPPORTED;
@@ -951,7 +978,10 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     p.window = window > 0 ? window : 0; p.chunk = chunk > 0 ? chunk : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.sink = sink;
-    if (gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;
+    p.dist = dist; p.keep_first = (keep_first > 0 && window > 0) ? keep_first : 0;
+    if (qkv && (dist || p.keep_first)) return BW_ERR_UNSUPPORTED;
+    if (gate && gate_dv < 0 ? (-gate_dv > HD || gate_ld < (long long)nh)
+                            : gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;
     p.gate = gate; p.gate_ld = gate_ld; p.gate_dv = gate_dv;
     p.qkv = qkv; p.qkv_plane_stride = qkv_plane_stride; p.rope_table = rope_table;
     p.qkv_planes = qkv_planes; p.rd = rd; p.append = append;
@@ -964,7 +994,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
         p.work = keys_work;
         bool launched = false;
 #if HEAD_DIM % 64 == 0
-        if (tma_keys) {
+        if (tma_keys && p.keep_first == 0) {   // (the TMA kernel walks one stretch of tiles: kept first keys take the other)
             static bool tma_attr_done[bw::MAX_DEVICES];
             if (cudaError_t e = bw::allow_dynamic_smem(attn_keys_tma_kernel, SMEM_KEYS_TMA, tma_attr_done); e != cudaSuccess) return (int)e;
             CUtensorMap tk, tv;

@@ -58,7 +58,7 @@ struct Params {
     float scale_log2;
     const float* sink;   // float32 [nh] or null: exp(sink[query head]) joins the row's softmax denominator (no key, no value, not scaled)
     // gate != null: output channel c < gate_dv of (token, head) times sigmoid(gate[token * gate_ld + head * gate_dv + c]),
-    // channels from gate_dv on zero (bw::out_gate)
+    // channels from gate_dv on zero (bw::out_gate); gate_dv < 0: one gate number per head, gate[token * gate_ld + head]
     const float* gate; long long gate_ld; int gate_dv;
 };
 
@@ -331,7 +331,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         // this row's 32 gate values lie side by side: 16-byte loads where the row allows them
                         const size_t token = (size_t)(p.cu_q[r] + tok0 + tok);
                         const float* grow = p.gate + token * (size_t)p.gate_ld + (size_t)(g * p.G + hg) * p.gate_dv + c0;
-                        if (c0 + 32 <= p.gate_dv && (((uintptr_t)grow) & 15) == 0) {
+                        if (p.gate_dv < 0) {   // one gate number per head, for the head's first -gate_dv channels
+                            const float gh = 1.f / (1.f + __expf(-__ldg(p.gate + token * (size_t)p.gate_ld + (size_t)(g * p.G + hg))));
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                v[c] = __float_as_uint(c0 + c < -p.gate_dv ? __uint_as_float(v[c]) * gh : 0.f);
+                        } else if (c0 + 32 <= p.gate_dv && (((uintptr_t)grow) & 15) == 0) {
 #pragma unroll
                             for (int c = 0; c < 32; c += 4) {
                                 const float4 gv = __ldg(reinterpret_cast<const float4*>(grow + c));
@@ -434,7 +439,8 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
     p.window = window > 0 ? window : 0; p.chunk = chunk > 0 ? chunk : 0; p.tpt = tpt;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.sink = sink;
-    if (gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;
+    if (gate && gate_dv < 0 ? (-gate_dv > HD || gate_ld < (long long)nh)
+                            : gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;
     p.gate = gate; p.gate_ld = gate_ld; p.gate_dv = gate_dv;
     bw::launch((attn_tc_kernel), dim3((unsigned)n_items * nkv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, tq, tk, tv, p);
     BW_LAUNCH_CHECK();

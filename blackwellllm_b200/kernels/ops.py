@@ -818,16 +818,17 @@ def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
     if q.dtype == torch.float32:
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
                               window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first)
-    if dist is not None or keep_first or (gate is not None and len(gate) > 2):
-        # the tensor-core kernels know neither: the CUDA-core kernel in bfloat16
+    if nh // k_pages.shape[1] > MAX_GROUP_BF16:
+        # more query heads per kv head than a tile of the tensor-core kernels stacks: the CUDA-core kernel in bfloat16
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
                               window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first)
-    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate)
+    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate, dist, keep_first)
 
 
 _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p]
+                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_int,
+                                   c_void_p, c_int, c_void_p]
 
 
 _sm_counts = {}
@@ -846,7 +847,7 @@ def num_sms(device=None) -> int:
 
 def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Optional[int], hd: int = 128,
                         rows_tile: int = 64, page_size: int = 16, static_bound: Optional[int] = None,
-                        sms: int = 148, chunk: Optional[int] = None):
+                        sms: int = 148, chunk: Optional[int] = None, keep_first: int = 0):
     """The work lists of the tensor-core attention as plain lists (host arithmetic only):
     ``rows`` items (request, first token, 0, 0) for segments of more than 16 stacked rows (tokens x
     heads of a group), cut into tiles of ``rows_tile`` rows and ordered longest first; ``keys`` items
@@ -873,8 +874,8 @@ def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Option
             rows_items += [(r, t0, 0, 0) for t0 in range(0, n_q, tpt)]
             continue
         span = static_bound or kv_len[r]
-        if window:
-            span = min(span, window + n_q)
+        if window:   # (kept first keys lie in tiles of their own before the window's)
+            span = min(span, window + n_q + (-(-keep_first // 64) * 64 if keep_first else 0))
         if chunk:   # a query sees no key before the start of its block of positions
             span = min(span, chunk + n_q)
         tiles = -(-span // 64)
@@ -889,18 +890,18 @@ def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Option
 
 
 def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128, rows_tile: int = 64,
-                   page_size: int = 16, chunk: Optional[int] = None):
+                   page_size: int = 16, chunk: Optional[int] = None, keep_first: int = 0):
     """The work lists of :func:`plan_attention_work` for this batch and group size on the device,
     made once per step and shared by all layers.  With ``batch.static_bound`` (graph replay) the
     number of key slices depends on that bound, not on the lengths."""
-    key = ("attn_work", G, nkv, window, hd, rows_tile, page_size, chunk)
+    key = ("attn_work", G, nkv, window, hd, rows_tile, page_size, chunk, keep_first)
     cached = batch.static_extras.get(key)
     if cached is not None:
         return cached
     R = batch.R
     rows_items, keys_items, merge_items, total_slices = plan_attention_work(
         batch.h_q_len[:R], batch.h_q_start[:R], batch.h_kv_len[:R], G, nkv, window, hd, rows_tile, page_size,
-        batch.static_bound, num_sms(batch.token_ids.device), chunk)
+        batch.static_bound, num_sms(batch.token_ids.device), chunk, keep_first)
     dev = batch.token_ids.device
 
     def up(items):
@@ -916,9 +917,12 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
 
 def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_table: torch.Tensor,
                   nh: int, window: Optional[int], scale: float, chunk: Optional[int] = None,
-                  sink: Optional[torch.Tensor] = None, gate: Optional[tuple] = None) -> torch.Tensor:
+                  sink: Optional[torch.Tensor] = None, gate: Optional[tuple] = None,
+                  dist: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
     _check_sink(sink, nh)
+    _check_dist(dist, nh)
+    keep_first = int(keep_first or 0) if window else 0
     g, g_ld, g_dv = _gate_args(gate, batch.T, nh, k_pages.shape[3])
     _dev(block_table, "block_table", torch.int32)
     num_pages, nkv, page_size, hd = k_pages.shape
@@ -945,9 +949,10 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
     G = nh // nkv
     check_attention_supported(torch.bfloat16, hd, G)
     # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
-    use_tc = attention_tc_supports(hd, G, page_size)
+    # (a distance bias or kept first keys: the mma.sync kernels)
+    use_tc = attention_tc_supports(hd, G, page_size) and dist is None and not keep_first
     rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices, merge_max = attention_work(
-        batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64, page_size=page_size, chunk=chunk)
+        batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64, page_size=page_size, chunk=chunk, keep_first=keep_first)
     part_o = part_ml = None
     if n_merge:
         part_o = torch.empty((slices * nkv * 16, hd), dtype=torch.float32, device=out.device)
@@ -970,7 +975,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
               _ptr(raw.planes if raw is not None else None), raw.planes.shape[0] if raw is not None else 0,
               raw.planes.stride(0) if raw is not None else 0, _ptr(raw.table if raw is not None else None),
               raw.rotary_dim if raw is not None else 0, int(raw.append) if raw is not None else 0, merge_max,
-              _ptr(sink), _ptr(g), g_ld, g_dv, _stream()), "attention_mma")
+              _ptr(sink), _ptr(g), g_ld, g_dv, _ptr(dist), keep_first, _stream()), "attention_mma")
     return out
 
 

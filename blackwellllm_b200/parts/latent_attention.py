@@ -49,7 +49,8 @@ class LatentAttention(Mixer):
             raise ValueError(f"rot_dim {self.dr} must be even and positive")
         step = 16 if ctx.dtype == torch.bfloat16 else 1
         self.dpad = -(-(self.rank + self.dr) // step) * step      # the cached row, in steps the attention kernels take
-        ops.check_attention_supported(ctx.dtype, self.dpad, self.H)   # all heads share the one key/value head
+        ops.check_attention_supported(ctx.dtype, self.dpad)   # (all heads share the one key/value head: beyond what a
+                                                               # tile of the tensor-core kernels stacks, the CUDA-core kernel runs)
         self.position = build_position(spec.position, self.dr, ctx)
         if getattr(self.position, "rotary_dim", None) != self.dr or getattr(self.position, "interleaved", False):
             raise ValueError("latent attention turns all rot_dim channels, channel i with channel i + rot_dim / 2")
