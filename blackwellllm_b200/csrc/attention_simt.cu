@@ -14,9 +14,9 @@ using bf16 = __nv_bfloat16;
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_CH = 8;  // channels per lane: head_dim <= 256
+constexpr int HD_LIMIT = 1024;   // the kernel is built for 8 channels a lane (head sizes up to 256) and for 32 (up to 1024)
 
-template <typename QT, typename KT, typename OT>
+template <typename QT, typename KT, typename OT, int MAX_CH>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
                       const KT* __restrict__ v_pages, const int* __restrict__ positions,
@@ -128,18 +128,16 @@ BW_EXPORT int bw_attention_simt(const void* q, const void* k_pages, const void* 
                                 int num_pages, int window, int chunk, float scale, const float* sink, const float* gate,
                                 long long gate_ld, int gate_dv, const float* dist, int keep_first, void* stream) {
     if (T <= 0) return 0;
-    if (hd <= 0 || hd > 32 * MAX_CH || nkv <= 0 || nh % nkv != 0) return BW_ERR_UNSUPPORTED;
+    if (hd <= 0 || hd > HD_LIMIT || nkv <= 0 || nh % nkv != 0) return BW_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, nh);
     const size_t smem = (size_t)(hd + WARPS * hd + WARPS * 2) * sizeof(float);
-    if (type == BW_F32)
-        attention_simt_kernel<float, float, float><<<grid, WARPS * 32, smem, s>>>(
-            (const float*)q, (const float*)k_pages, (const float*)v_pages, positions, req_of_token,
-            block_table, max_blocks, (float*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv, dist, keep_first);
-    else if (type == BW_BF16)
-        attention_simt_kernel<bf16, bf16, bf16><<<grid, WARPS * 32, smem, s>>>(
-            (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, positions, req_of_token,
-            block_table, max_blocks, (bf16*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv, dist, keep_first);
+#define BW_SIMT(TY, CH) attention_simt_kernel<TY, TY, TY, CH><<<grid, WARPS * 32, smem, s>>>( \
+        (const TY*)q, (const TY*)k_pages, (const TY*)v_pages, positions, req_of_token, block_table, max_blocks, (TY*)out, nh, \
+        nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv, dist, keep_first)
+    if (type == BW_F32) { if (hd <= 256) BW_SIMT(float, 8); else BW_SIMT(float, 32); }
+    else if (type == BW_BF16) { if (hd <= 256) BW_SIMT(bf16, 8); else BW_SIMT(bf16, 32); }
+#undef BW_SIMT
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;

@@ -88,6 +88,8 @@ __device__ __forceinline__ float ep_glu(const Epilogue& ep, float g, float u) {
         u = fminf(fmaxf(u, -ep.act_limit), ep.act_limit) + 1.f;
         return __fdividef(g, 1.f + __expf(-ep.act_alpha * g)) * u;
     }
+    if (ep.act == BW_ACT_GELU_TANH)   // 0.5 g (1 + tanh z) = g sigmoid(2 z), z = sqrt(2 / pi) (g + 0.044715 g^3)
+        return __fdividef(g, 1.f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g))) * u;
     return __fdividef(g, 1.f + __expf(-g)) * u;
 }
 __device__ __forceinline__ float ep_unary(const Epilogue& ep, float v) {
@@ -207,15 +209,17 @@ __device__ __forceinline__ void emit(const Epilogue& ep, float* part, const floa
         return;
     }
     if (ep.swiglu) {
-        // lanes 0..15 hold gate, lanes 16..31 up of the same 16 output features
+        // lanes 0..15 hold gate, lanes 16..31 up of the same 16 output features (each adds its own row's bias)
         const int lane = threadIdx.x & 31;
         const int j = (feature / (2 * SWIGLU_BLOCK)) * SWIGLU_BLOCK + lane;
+        const float b = fvalid ? bias_at(ep, feature) : 0.f;
 #pragma unroll
         for (int c = 0; c < N; ++c) {
-            const float other = __shfl_xor_sync(0xffffffffu, vals[c], 16);
+            const float mine = vals[c] + b;
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
             if (c < nvalid && fvalid && lane < SWIGLU_BLOCK)
                 ((bf16*)ep.out)[(size_t)(token0 + c) * ep.ldo + j] =
-                    __float2bfloat16_rn(ep_glu(ep, vals[c], other));
+                    __float2bfloat16_rn(ep_glu(ep, mine, other));
         }
         return;
     }
@@ -326,7 +330,7 @@ __device__ __forceinline__ void swiglu_direct(const Epilogue& ep, const uint32_t
     float y[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        const float g = __uint_as_float(v[i]), u = __uint_as_float(v[16 + i]);
+        const float g = __uint_as_float(v[i]) + bias_at(ep, f0 + i), u = __uint_as_float(v[16 + i]) + bias_at(ep, f0 + 16 + i);
         y[i] = ep_glu(ep, g, u);
     }
     bf16* dst = (bf16*)ep.out + (size_t)token * ep.ldo + (f0 / (2 * SWIGLU_BLOCK)) * SWIGLU_BLOCK;
@@ -919,7 +923,7 @@ __global__ void splitk_reduce_kernel(Epilogue ep) {
         const int token = (int)(i / width), j = (int)(i - (size_t)token * width);
         if (ep.swiglu) {
             const int fg = (j / SWIGLU_BLOCK) * 2 * SWIGLU_BLOCK + j % SWIGLU_BLOCK, fu = fg + SWIGLU_BLOCK;
-            float g = 0.f, u = 0.f;
+            float g = bias_at(ep, fg), u = bias_at(ep, fu);
             for (int s = 0; s < ep.splits; ++s) {
                 g += ep.partial[(size_t)s * plane + (size_t)token * ep.features + fg];
                 u += ep.partial[(size_t)s * plane + (size_t)token * ep.features + fu];
@@ -1139,8 +1143,8 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
                        int force_splits, const RopeOut* rope, void* stream, int* planes_out = nullptr,
                        int act = 0, float act_limit = 0.f, float act_alpha = 1.f) {
     if (M <= 0 || N <= 0) return 0;
-    // act: with swiglu the gated activation (BW_ACT_SILU or BW_ACT_CLAMPED_SWISH); without, 0 or BW_ACT_RELU2 on the sums
-    if (swiglu ? (act != BW_ACT_SILU && act != BW_ACT_CLAMPED_SWISH) : (act != 0 && act != BW_ACT_RELU2)) return BW_ERR_BAD_ARG;
+    // act: with swiglu the gated activation (BW_ACT_SILU, BW_ACT_CLAMPED_SWISH or BW_ACT_GELU_TANH); without, 0 or BW_ACT_RELU2 on the sums
+    if (swiglu ? (act != BW_ACT_SILU && act != BW_ACT_CLAMPED_SWISH && act != BW_ACT_GELU_TANH) : (act != 0 && act != BW_ACT_RELU2)) return BW_ERR_BAD_ARG;
     if (!swiglu && act != 0 && (accumulate || rope || planes_out)) return BW_ERR_BAD_ARG;
     // planes_out: the product is left as *planes_out float32 planes [M, N] in `out` (row stride N, the bias
     // in the first), to be added up by its reader; K is split as if the sums were made here.
@@ -1151,7 +1155,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     const int NUM_SMS = bw::num_sms();
     if (!bw_gemm_tc_supported(x, w, K, ldx)) return BW_ERR_UNSUPPORTED;
     if (accumulate && out_type != BW_F32) return BW_ERR_BAD_ARG;
-    if (swiglu && (N % (2 * SWIGLU_BLOCK) != 0 || out_type != BW_BF16 || accumulate || bias || ldo < N / 2))
+    if (swiglu && (N % (2 * SWIGLU_BLOCK) != 0 || out_type != BW_BF16 || accumulate || ldo < N / 2))
         return BW_ERR_BAD_ARG;
     if (rope && (swiglu || accumulate)) return BW_ERR_BAD_ARG;
     if (!swiglu && !rope && ldo < N) return BW_ERR_BAD_ARG;

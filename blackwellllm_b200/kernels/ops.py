@@ -315,8 +315,8 @@ def swiglu(gu: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.T
 ACT_SILU, ACT_CLAMPED_SWISH, ACT_RELU2, ACT_GELU_TANH = 0, 1, 2, 3   # the activation codes of csrc/common.cuh
 GATED_ACTIVATIONS = {"silu": ACT_SILU, "clamped_swish": ACT_CLAMPED_SWISH, "gelu_tanh": ACT_GELU_TANH}
 UNARY_ACTIVATIONS = {"relu2": ACT_RELU2}
-GEMM_TC_GATED_ACTIVATIONS = (ACT_SILU, ACT_CLAMPED_SWISH)   # what gemm_tc's fused gate/up epilogue computes
-GEMM_TC_GATED_BIAS = False                                  # ... and whether it takes biases on gate and up
+GEMM_TC_GATED_ACTIVATIONS = (ACT_SILU, ACT_CLAMPED_SWISH, ACT_GELU_TANH)   # what gemm_tc's fused gate/up epilogue computes
+GEMM_TC_GATED_BIAS = True                                   # ... and whether it takes biases on gate and up (interleaved like the rows)
 
 
 def glu(gu: torch.Tensor, act: int, limit: float = 0.0, alpha: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -647,7 +647,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     """out (=|+=) x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, float32 sums).
     ``swiglu``: ``w`` is a gate/up weight from :func:`interleave_gate_up`; the result is
     bfloat16 [M, N / 2] = silu(gate) * up, computed in the epilogue; ``act`` = ACT_CLAMPED_SWISH (with its
-    ``limit`` and ``alpha``) puts that gated activation in its place (:func:`glu`).  Without ``swiglu``,
+    ``limit`` and ``alpha``) or ACT_GELU_TANH puts that gated activation in its place (:func:`glu`); a ``bias`` (interleaved
+    like the rows) is added to gate and up before it.  Without ``swiglu``,
     ``act`` = ACT_RELU2 squares the positive part of every sum of a result that is written (not added)."""
     _dev(x, "x", torch.bfloat16, contiguous=False); _dev(w, "w", torch.bfloat16)
     if not gemm_tc_supports(x, w):
@@ -659,8 +660,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         raise KernelError(f"gemm: x has {K} columns, w has {K2}")
     n_out = N
     if swiglu:
-        if N % (2 * SWIGLU_BLOCK) or bias is not None or accumulate:
-            raise KernelError("gemm_tc: the SwiGLU epilogue needs N = 2 I with I a multiple of 16, no bias, no accumulate")
+        if N % (2 * SWIGLU_BLOCK) or accumulate:
+            raise KernelError("gemm_tc: the SwiGLU epilogue needs N = 2 I with I a multiple of 16 and no accumulate")
         n_out, out_dtype = N // 2, torch.bfloat16
     if out is None:
         if accumulate:
@@ -763,13 +764,14 @@ def gemm_tc_status() -> int:
     return int(lib.bw_gemm_tc_status())
 
 
+ATTENTION_SIMT_MAX_HEAD_DIM = 1024   # the CUDA-core kernel's limit; the tensor-core kernels are built for head sizes up to 256
 MAX_GROUP_BF16 = 16   # query heads per kv head that the bfloat16 attention kernels stack in one tile
 
 
 def check_attention_supported(dtype: torch.dtype, head_dim: int, group: int = 1) -> None:
     """Raises for a geometry no attention kernel of this dtype takes (known when a model is built)."""
-    if head_dim <= 0 or head_dim > 256:
-        raise KernelError(f"attention: head_dim {head_dim} is not supported (1..256)")
+    if head_dim <= 0 or head_dim > ATTENTION_SIMT_MAX_HEAD_DIM:
+        raise KernelError(f"attention: head_dim {head_dim} is not supported (1..{ATTENTION_SIMT_MAX_HEAD_DIM})")
     if dtype == torch.bfloat16 and head_dim % 16:
         raise KernelError(f"attention: the bfloat16 kernels take head sizes in steps of 16, got {head_dim}")
     if dtype == torch.bfloat16 and group > MAX_GROUP_BF16:
@@ -818,8 +820,9 @@ def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
     if q.dtype == torch.float32:
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
                               window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first)
-    if nh // k_pages.shape[1] > MAX_GROUP_BF16:
-        # more query heads per kv head than a tile of the tensor-core kernels stacks: the CUDA-core kernel in bfloat16
+    if nh // k_pages.shape[1] > MAX_GROUP_BF16 or k_pages.shape[3] > 256:
+        # more query heads per kv head than a tile of the tensor-core kernels stacks, or a head size beyond the ones
+        # they are built for (a wide latent row): the CUDA-core kernel in bfloat16
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
                               window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first)
     return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate, dist, keep_first)
@@ -948,6 +951,8 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
         out = torch.empty_like(q)
     G = nh // nkv
     check_attention_supported(torch.bfloat16, hd, G)
+    if hd > 256:
+        raise KernelError(f"attention: the tensor-core kernels are built for head sizes up to 256, got {hd}")
     # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
     # (a distance bias or kept first keys: the mma.sync kernels)
     use_tc = attention_tc_supports(hd, G, page_size) and dist is None and not keep_first

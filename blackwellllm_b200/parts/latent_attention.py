@@ -51,6 +51,14 @@ class LatentAttention(Mixer):
         self.dpad = -(-(self.rank + self.dr) // step) * step      # the cached row, in steps the attention kernels take
         ops.check_attention_supported(ctx.dtype, self.dpad)   # (all heads share the one key/value head: beyond what a
                                                                # tile of the tensor-core kernels stacks, the CUDA-core kernel runs)
+        # heads per attention call: all of them, or in bfloat16 the largest divisor of their number that the tensor-core
+        # kernels stack on one key/value head (a number of heads without such a divisor of at least 4 runs in one call
+        # on the CUDA-core kernel)
+        self.heads_per_call = self.H
+        if ctx.dtype == torch.bfloat16 and self.H > ops.MAX_GROUP_BF16 and self.dpad <= 256:
+            n = max(k for k in range(1, ops.MAX_GROUP_BF16 + 1) if self.H % k == 0)
+            if n >= 4:
+                self.heads_per_call = n
         self.position = build_position(spec.position, self.dr, ctx)
         if getattr(self.position, "rotary_dim", None) != self.dr or getattr(self.position, "interleaved", False):
             raise ValueError("latent attention turns all rot_dim channels, channel i with channel i + rot_dim / 2")
@@ -84,13 +92,18 @@ class LatentAttention(Mixer):
     def forward(self, x, residual, batch, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         H, d, dr, rank = self.H, self.d, self.dr, self.rank
         proj = self.proj(x, out_dtype=torch.float32)       # [T, H * (d + dr) | rank + dr]
-        q = ops.latent_prep(proj, 0, H * (d + dr), batch, batch.block_tables[cache.group], self.position.table(batch),
-                            self.c_gain, self.eps, cache.k_pages, H, d, dr, rank, append=owns_cache)
-        ops.headwise_linear(proj, 0, d + dr, self.uk_t, q, 0, self.dpad)
-        o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group], H, self.window,
-                                self.scale, None, self.sink, None)
         y = torch.empty((x.shape[0], H * self.dv), dtype=x.dtype, device=x.device)
-        ops.headwise_linear(o, 0, self.dpad, self.uv, y, 0, self.dv)
+        table, bt = self.position.table(batch), batch.block_tables[cache.group]
+        # all heads share the one cached row; the tensor-core kernels stack up to ops.MAX_GROUP_BF16 query heads on a
+        # key/value head, so more heads than that run as several groups of heads over the same rows
+        n = self.heads_per_call
+        for h0 in range(0, H, n):
+            q = ops.latent_prep(proj, h0 * (d + dr), H * (d + dr), batch, bt, table, self.c_gain, self.eps, cache.k_pages,
+                                n, d, dr, rank, append=owns_cache and h0 == 0)
+            ops.headwise_linear(proj, h0 * (d + dr), d + dr, self.uk_t[h0:h0 + n], q, 0, self.dpad)
+            o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, bt, n, self.window, self.scale, None,
+                                    None if self.sink is None else self.sink[h0:h0 + n], None)
+            ops.headwise_linear(o, 0, self.dpad, self.uv[h0:h0 + n], y, h0 * self.dv, self.dv)
         if accumulate:
             self.o.add_to(y, residual)
         elif accumulate is None:

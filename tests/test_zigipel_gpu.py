@@ -119,6 +119,34 @@ def test_two_streams_side_by_side_and_gated_gelu(ops, dtype):
     assert float((got - want).abs().max()) <= (1e-6 if dtype == torch.float32 else 1e-2) * float(want.abs().max())
 
 
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+@pytest.mark.parametrize("T", [1, 8, 16, 17, 100, 300, 600, 1100])
+@pytest.mark.parametrize("H,F", [(64, 96), (256, 1024), (2048, 512)])
+def test_dense_feed_forward_with_biases_bfloat16(ops, act, T, H, F):
+    """The gated feed-forward part on the tensor cores: the gate/up product adds the biases and applies the activation
+    in its epilogue, in every form of that product (few tokens with the K splits summed in the kernel, split K with a
+    second kernel, whole tiles, CTA pairs)."""
+    from blackwellllm_b200.config.specs import SwiGLUSpec
+    from blackwellllm_b200.parts import BuildContext, build_ffn
+    spec = SwiGLUSpec(intermediate_size=F, activation=act, names=("gate", "up", "down"), bias_names=("gate.b", "up.b", "down.b"))
+    ffn = build_ffn(spec, H, BuildContext(DEV, torch.bfloat16))
+    t = {"gate": rnd(F, H, seed=1, scale=H ** -0.5), "up": rnd(F, H, seed=2, scale=H ** -0.5), "down": rnd(H, F, seed=3, scale=F ** -0.5),
+         "gate.b": rnd(F, seed=4), "up.b": rnd(F, seed=5), "down.b": rnd(H, seed=6)}
+    t = {k: v.to(torch.bfloat16) for k, v in t.items()}
+    ffn.bind({k: d(v) for k, v in t.items()})
+    assert ffn.fused
+    x = rnd(T, H, seed=7).to(torch.bfloat16)
+    res = torch.zeros(T, H, device=DEV)
+    ffn.forward(d(x), res, None)
+    ops.resolve_pending()
+    w = {k: v.double() for k, v in t.items()}
+    g, u = x.double() @ w["gate"].T + w["gate.b"], x.double() @ w["up"].T + w["up.b"]
+    a = plain.gelu_tanh(g) * u if act == "gelu_tanh" else g * torch.sigmoid(g) * u
+    want = a @ w["down"].T + w["down.b"]
+    assert float((res.cpu().double() - want).abs().max()) <= 1.5e-2 * float(want.abs().max())
+    assert ops.gemm_tc_status() == 0
+
+
 def _biased_attention(q, k, v, sink, scale, r1, r2, window, keep, gate=None):
     """q [L, nh, hd], k / v [L, nkv, hd] float64 -> [L, nh, hd]: the plain implementation's pieces."""
     L, nh, _ = q.shape
@@ -254,10 +282,11 @@ def test_values_are_cached_with_unit_root_mean_square(ops, out_dtype, nh, nkv, d
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,d_,dr,dv,rank,page,window", [(2, 16, 8, 24, 40, 8, 9), (3, 8, 16, 8, 24, 16, 30), (4, 32, 32, 48, 96, 16, None),
-                                                         (20, 12, 12, 20, 24, 32, 50)])
+                                                         (20, 12, 12, 20, 24, 32, 50), (2, 16, 16, 24, 272, 16, 40), (17, 8, 8, 8, 24, 8, 20)])
 def test_latent_attention_mixer_alone(ops, dtype, H, d_, dr, dv, rank, page, window):
     """The mixer part against the plain function: a prompt in two portions and then single tokens, next to another
-    request; the cache holds one row of rank + rot_dim channels per token (one plane); 20 heads share it."""
+    request; the cache holds one row of rank + rot_dim channels per token (one plane); 20 heads share it (two groups of 10 on the tensor cores) or 17 (one call); a latent
+    row wider than the tensor-core kernels' head sizes."""
     from blackwellllm_b200.config.specs import LatentAttentionSpec, RopeSpec, YarnRopeScaling
     from blackwellllm_b200.parts import BuildContext, build_mixer
     from test_kernels_gpu import FakeBatch
