@@ -355,7 +355,33 @@ FUVEVIK_SHAPES = {
     "2k": (2048, 16, 4, 128, 4, 8192, 16, 2, 4, 1024, 1024, 32000, 2),
     "4k": (4096, 32, 8, 128, 4, 14336, 8, 1, 2, 3584, 3584, 32000, 2),
 }
-DESIGNS = {"gafulix": (_gafulix_shape, DESIGN_SHAPES), "fuvevik": (_fuvevik_shape, FUVEVIK_SHAPES)}
+def _zigipel_shape(width, heads, kv, hd, window, keep, l_heads, l_dim, l_rot, l_vdim, l_rank, ff, vocab, pairs, times):
+    """``pairs`` times (an attention layer, a latent-attention layer), each with a dense gated feed-forward, the whole
+    stretch run ``times`` times; and the dense decoder of equal width, heads, feed-forward size and number of layer
+    RUNS (its layers are all distinct: the same work a step, more weights to read)."""
+    att = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window, "keep_first": keep}}
+    lat = {"heads": l_heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "kv_rank": l_rank, "scale": (l_dim + l_rot) ** -0.5,
+           "mask": {"size": window},
+           "rot": {"base": 10000.0, "dims": l_rot, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = [{"type": "attention", "mixer": att, "mlp": mlp}, {"type": "latent_attention", "mixer": lat, "mlp": mlp}] * pairs
+    design = {"architecture": "Zigipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+              "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+              "loop": {"start": 0, "stop": 2 * pairs, "times": times}, "layers": layers}
+    dense = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": width,
+             "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd, "intermediate_size": ff,
+             "num_hidden_layers": 2 * pairs * times, "vocab_size": vocab, "rope_theta": 10000.0, "rms_norm_eps": 1e-5}
+    return design, dense
+
+
+ZIGIPEL_SHAPES = {
+    # width, heads, kv heads, head size, window, kept first keys, latent: heads, plain size, rotated size, value size, rank,
+    # feed-forward size, vocab, layer pairs, passes
+    "2k": (2048, 16, 4, 128, 1024, 4, 16, 128, 64, 128, 192, 5632, 32000, 1, 2),
+    "4k": (4096, 32, 8, 128, 1024, 4, 32, 128, 64, 128, 192, 11008, 32000, 1, 2),
+}
+DESIGNS = {"gafulix": (_gafulix_shape, DESIGN_SHAPES), "fuvevik": (_fuvevik_shape, FUVEVIK_SHAPES),
+           "zigipel": (_zigipel_shape, ZIGIPEL_SHAPES)}
 
 
 def design_comparison(args):

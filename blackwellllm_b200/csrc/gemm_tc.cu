@@ -328,10 +328,31 @@ __device__ __forceinline__ void rope_direct(const Epilogue& ep, const uint32_t (
 // It writes silu(gate) * up for those 16 features as 32 contiguous bytes.
 __device__ __forceinline__ void swiglu_direct(const Epilogue& ep, const uint32_t (&v)[32], int token, int f0) {
     float y[16];
+    if (ep.bias) {
+        // the 32 biases of these features lie side by side (the same for every lane): 16-byte loads where they allow it
+        float b[32];
+        if (ep.bias_type == BW_F32 && (((uintptr_t)ep.bias) & 15) == 0) {
+            const float4* src = reinterpret_cast<const float4*>((const float*)ep.bias + f0);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float g = __uint_as_float(v[i]) + bias_at(ep, f0 + i), u = __uint_as_float(v[16 + i]) + bias_at(ep, f0 + 16 + i);
-        y[i] = ep_glu(ep, g, u);
+            for (int i = 0; i < 8; ++i) { const float4 t = __ldg(src + i); b[4 * i] = t.x; b[4 * i + 1] = t.y; b[4 * i + 2] = t.z; b[4 * i + 3] = t.w; }
+        } else if (ep.bias_type != BW_F32 && (((uintptr_t)ep.bias) & 15) == 0) {
+            const uint4* src = reinterpret_cast<const uint4*>((const bf16*)ep.bias + f0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 t = __ldg(src + i);
+                const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { b[8 * i + 2 * k] = __uint_as_float(w[k] << 16); b[8 * i + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) b[i] = bias_at(ep, f0 + i);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = ep_glu(ep, __uint_as_float(v[i]) + b[i], __uint_as_float(v[16 + i]) + b[16 + i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = ep_glu(ep, __uint_as_float(v[i]), __uint_as_float(v[16 + i]));
     }
     bf16* dst = (bf16*)ep.out + (size_t)token * ep.ldo + (f0 / (2 * SWIGLU_BLOCK)) * SWIGLU_BLOCK;
     if ((ep.ldo & 7) == 0 && ((uintptr_t)ep.out & 15) == 0) {

@@ -6,7 +6,8 @@
 //   * latent_prep: RMS norm of the latent with its gain, rotation of the shared key part and of the queries' rotated
 //     parts, append of [c, k_rot, 0...] to the token's cache row;
 //   * headwise_linear: y[t, h, :] = W[h] x[t, h, :] for every head h (a small product per head: W_uk,h^T on the queries,
-//     W_uv,h on the attention's output), float32 sums in a fixed order.
+//     W_uv,h on the attention's output), float32 sums in a fixed order: on the CUDA cores in float32, on the tensor
+//     cores (mma.sync) with bfloat16 weights.
 #include "common.cuh"
 
 using bf16 = __nv_bfloat16;
@@ -106,6 +107,101 @@ headwise_linear_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const 
     }
 }
 
+// The same product on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 sums) for bfloat16 weights and
+// results: a CTA of 4 warps makes 64 tokens x 64 outputs of one head, warp w the tokens 16 w .. 16 w + 15; the operands
+// pass through shared memory 64 inner values at a time (float32 inputs are rounded to bfloat16 on the way; 16-byte
+// loads where sizes and addresses allow them: `vec`), rows padded to 144 bytes so that the 8 rows of an ldmatrix fall into different banks.
+constexpr int MT = 64, MO = 64, MK = 64, MROW = (MK + 8) * 2;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(128)
+headwise_mma_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const bf16* __restrict__ w, bf16* __restrict__ y,
+                    long long ldy, int y_hs, int T, int n_in, int n_out, int vec) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    __shared__ __align__(16) uint8_t xs[MT * MROW];
+    __shared__ __align__(16) uint8_t ws[MO * MROW];
+    const int h = blockIdx.z, t0 = blockIdx.x * MT, o0 = blockIdx.y * MO;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bf16* wh = w + (size_t)h * n_out * n_in;
+    float acc[MO / 8][4];
+#pragma unroll
+    for (int j = 0; j < MO / 8; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+    // every thread stages 32 inner values of one row of each operand, 8 at a time
+    const int srow = threadIdx.x >> 1, scol = (threadIdx.x & 1) * 32;
+    for (int k0 = 0; k0 < n_in; k0 += MK) {
+        const int t = t0 + srow, o = o0 + srow;
+        const XT* src = x + (size_t)(t < T ? t : 0) * ldx + (size_t)h * x_hs + k0 + scol;
+        const bf16* wsrc = wh + (size_t)(o < n_out ? o : 0) * n_in + k0 + scol;
+        uint8_t* dst = xs + srow * MROW + scol * 2;
+        uint8_t* wdst = ws + srow * MROW + scol * 2;
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+            const bool in = k0 + scol + c < n_in;      // (vec: n_in is a multiple of 8, so a chunk is inside or outside)
+            uint4 xv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
+            if (vec) {
+                if (in && t < T) {
+                    if constexpr (sizeof(XT) == 4) {
+                        const float4 lo = *reinterpret_cast<const float4*>(src + c), hi = *reinterpret_cast<const float4*>(src + c + 4);
+                        xv = make_uint4(bw::pack_bf16x2(lo.x, lo.y), bw::pack_bf16x2(lo.z, lo.w), bw::pack_bf16x2(hi.x, hi.y), bw::pack_bf16x2(hi.z, hi.w));
+                    } else {
+                        xv = *reinterpret_cast<const uint4*>(src + c);
+                    }
+                }
+                if (in && o < n_out) wv = __ldg(reinterpret_cast<const uint4*>(wsrc + c));
+            } else {
+                bf16 xe[8], we[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const bool ok = k0 + scol + c + i < n_in;
+                    xe[i] = (ok && t < T) ? bw::from_f32<bf16>(bw::to_f32(src[c + i])) : __float2bfloat16_rn(0.f);
+                    we[i] = (ok && o < n_out) ? wsrc[c + i] : __float2bfloat16_rn(0.f);
+                }
+                xv = *reinterpret_cast<const uint4*>(xe);
+                wv = *reinterpret_cast<const uint4*>(we);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 2) = xv;
+            *reinterpret_cast<uint4*>(wdst + c * 2) = wv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < MK / 16; ++ks) {
+            uint32_t a[4];
+            ldsm_x4(smem_addr(xs) + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * MROW + 16 * (lane >> 4) + ks * 32,
+                    a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int nb = 0; nb < MO / 16; ++nb) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(smem_addr(ws) + (nb * 16 + (lane & 7) + 8 * (lane >> 4)) * MROW + 16 * ((lane >> 3) & 1) + ks * 32, b0, b1, b2, b3);
+                mma_bf16(acc[2 * nb], a, b0, b1);
+                mma_bf16(acc[2 * nb + 1], a, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int t = t0 + warp * 16 + (lane >> 2) + 8 * half;
+        if (t >= T) continue;
+        bf16* dst = y + (size_t)t * ldy + (size_t)h * y_hs;
+#pragma unroll
+        for (int j = 0; j < MO / 8; ++j) {
+            const int o = o0 + j * 8 + 2 * (lane & 3);
+            if (o < n_out) dst[o] = __float2bfloat16_rn(acc[j][2 * half]);
+            if (o + 1 < n_out) dst[o + 1] = __float2bfloat16_rn(acc[j][2 * half + 1]);
+        }
+    }
+}
+
 }  // namespace
 
 // proj: float32 rows `ld` apart; queries at column q_off, H heads of (d plain, dr rotated) channels; the latent's
@@ -144,9 +240,15 @@ BW_EXPORT int bw_headwise_linear(const void* x, int x_type, long long ldx, int x
     const dim3 grid((T + HT - 1) / HT, (n_out + HO - 1) / HO, H);
 #define BW_HW(XT, WT, YT) bw::launch((headwise_linear_kernel<XT, WT, YT>), grid, dim3(256), 0, s, (const XT*)x, ldx, x_hs, \
         (const WT*)w, (YT*)y, ldy, y_hs, T, n_in, n_out)
+    const dim3 mgrid((T + MT - 1) / MT, (n_out + MO - 1) / MO, H);
+    // 16-byte loads: 8 inner values of a row at a time, every row starting on a 16-byte boundary
+    const int xe = x_type == BW_F32 ? 4 : 8;      // elements of x in 16 bytes
+    const int vec = n_in % 8 == 0 && ldx % xe == 0 && x_hs % xe == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
     if (x_type == BW_F32 && w_type == BW_F32 && y_type == BW_F32) BW_HW(float, float, float);
-    else if (x_type == BW_F32 && w_type == BW_BF16 && y_type == BW_BF16) BW_HW(float, bf16, bf16);
-    else if (x_type == BW_BF16 && w_type == BW_BF16 && y_type == BW_BF16) BW_HW(bf16, bf16, bf16);
+    else if (x_type == BW_F32 && w_type == BW_BF16 && y_type == BW_BF16)      // bfloat16 weights and results: the tensor cores
+        bw::launch((headwise_mma_kernel<float>), mgrid, dim3(128), 0, s, (const float*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec);
+    else if (x_type == BW_BF16 && w_type == BW_BF16 && y_type == BW_BF16)
+        bw::launch((headwise_mma_kernel<bf16>), mgrid, dim3(128), 0, s, (const bf16*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec);
     else return BW_ERR_UNSUPPORTED;
 #undef BW_HW
     BW_LAUNCH_CHECK();

@@ -103,7 +103,9 @@ class GQAAttention(Mixer):
         self.scale = float(spec.softmax_scale) if spec.softmax_scale is not None else self.hd ** -0.5
         self.ctx = ctx
         self.position = build_position(spec.position, self.hd, ctx)
-        ops.check_attention_supported(ctx.dtype, self.dpad, self.nh // self.nkv)
+        # (the general route hands ops.paged_attention finished queries: beyond the query heads per kv head that the
+        # tensor-core kernels stack, it takes the CUDA-core kernel; the fused route goes to the tensor-core kernels only)
+        ops.check_attention_supported(ctx.dtype, self.dpad, 1 if self.general else self.nh // self.nkv)
         self.qkv: Linear = None
         self.project = None
         self.o: Linear = None
