@@ -60,9 +60,19 @@ struct Params {
     // gate != null: output channel c < gate_dv of (token, head) times sigmoid(gate[token * gate_ld + head * gate_dv + c]),
     // channels from gate_dv on zero (bw::out_gate); gate_dv < 0: one gate number per head, gate[token * gate_ld + head]
     const float* gate; long long gate_ld; int gate_dv;
+    // dist != null: float32 [2][nh] (r1 of every query head, then r2): r1 ln(1 + r2 (i - j)) is taken off the score of
+    // query position i and key position j.  keep_first: with a window, the first so many keys of a sequence stay visible.
+    const float* dist; int keep_first;
 };
 
-// 2^x, one MUFU instruction (the flush of denormal results to zero does not matter for softmax weights)
+// 2^x and log2(x), one MUFU instruction each
+__device__ __forceinline__ float fast_log2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// (the flush of denormal results to zero does not matter for softmax weights)
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -126,7 +136,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int q_pos0 = p.q_start[r] + tok0;
     const int last_pos = q_pos0 + ntok - 1;
     const int first_key = bw::first_visible(q_pos0, p.window, p.chunk);
-    const int t_lo = first_key / BN, n_tiles = last_pos / BN - t_lo + 1;
+    // the walk over key tiles: the tiles that hold kept first keys and lie before the window's first tile, then
+    // the tiles from the window's first on
+    const int t_lo = first_key / BN;
+    const int kept = p.keep_first > 0 ? min((p.keep_first + BN - 1) / BN, t_lo) : 0;
+    const int n_tiles = kept + last_pos / BN - t_lo + 1;
+    auto tile_of = [&](int i) { return i < kept ? i : t_lo + (i - kept); };
     const int* bt = p.block_table + (size_t)r * p.max_blocks;
 
     if (dead) {
@@ -143,7 +158,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // latency is off the path) and its boxes are issued beside the other lanes'.
         const int ppt = BN / p.page_size;   // pages per tile
         auto lookup = [&](int i) {
-            const int key = (t_lo + i) * BN + lane * p.page_size;
+            const int key = tile_of(i) * BN + lane * p.page_size;
             int page = (lane < ppt && i < n_tiles && key < kv_len) ? bt[key / p.page_size] : -1;
             return page < 0 ? 0 : page;      // never read: a resident page keeps the tile finite
         };
@@ -229,12 +244,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         float m = -INFINITY, l = 0.f;   // m: the reference of the exponents (at most 8 below the row maximum)
         bool ok = true;
+        float r1 = 0.f, r2 = 0.f;
+        if (p.dist && row_ok) { r1 = p.dist[g * p.G + hg]; r2 = p.dist[p.nh + g * p.G + hg]; }
+        const float sc = p.dist ? 1.f : p.scale_log2;   // what turns a kept score into a power of two
 
         for (int i = 0; i < n_tiles; ++i) {
             if (!__all_sync(0xffffffffu, bw::mbar_wait(s_full + 8 * (i & 1), (i >> 1) & 1, &g_status, 16))) { ok = false; break; }
             bw::tc_fence_after();
-            const int key0 = (t_lo + i) * BN;
-            const bool need_mask = !row_ok || (key0 + BN - 1 > q_pos0) || (key0 < bw::first_visible(last_pos, p.window, p.chunk));
+            const int key0 = tile_of(i) * BN;
+            const bool need_mask = !row_ok || i < kept || (key0 + BN - 1 > q_pos0) || (key0 < bw::first_visible(last_pos, p.window, p.chunk));
             // The row of S, unscaled (scale > 0, so the maximum commutes with it; masked keys become -inf).
             // It stays in these 64 registers; the packed probabilities take the place of the first 32
             // as they are made, so that the kernel stays within 128 registers (see the launch bounds).
@@ -243,18 +261,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             bw::tmem_ld_32x32(s_row, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             bw::tmem_ld_32x32(s_row + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
             bw::tmem_ld_wait();
+            if (p.dist) {
+                // (uniform over the launch) the scores in powers of two with the distance bias taken off:
+                // s scale log2(e) - r1 log2(1 + r2 d); from here on the row is scaled already (sc = 1)
+                const float d0 = (float)(qpos - key0);
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const float b = fast_log2(fmaf(r2, fmaxf(d0 - (float)c, 0.f), 1.f));
+                    v[c] = __float_as_uint(fmaf(-r1, b, __uint_as_float(v[c]) * p.scale_log2));
+                }
+            }
             if (need_mask) {   // one branch per tile, not one per key
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int kp = key0 + c;
-                    if (!row_ok || kp > qpos || kp < lo) v[c] = 0xff800000u;   // -inf
+                    if (!row_ok || kp > qpos || (kp < lo && kp >= p.keep_first)) v[c] = 0xff800000u;   // -inf
                 }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c = 0; c < BN; c += 2)   // max(m, a, b): one three-input instruction where the hardware has it
                 mx4[(c >> 1) & 3] = fmaxf(mx4[(c >> 1) & 3], fmaxf(__uint_as_float(v[c]), __uint_as_float(v[c + 1])));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
             const bool grow = mx > m + 8.f;   // also the first finite maximum of a row (m is -inf until then)
             float factor = 1.f;
             if (grow) {
@@ -284,8 +312,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < BN; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), p.scale_log2, -mu));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), p.scale_log2, -mu));
+                const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), sc, -mu));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), sc, -mu));
                 sum4[(c >> 1) & 3] += p0 + p1;
                 v[c >> 1] = pack_bf16(p0, p1);
             }
@@ -409,11 +437,12 @@ BW_EXPORT int bw_attention_tc_supported(int nh, int nkv, int page_size) {
 
 // work: n_items int4 (request, first token of the 128-row tile within the request's segment, 0, 0);
 // a tile holds 128 / G tokens.  q, out: [T, nh * HD] bf16; pages: [num_pages, nkv, page_size, HD] bf16.
+// dist: float32 [2][nh] or null; keep_first: see Params.
 BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
                               const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
                               const int* work, int n_items, int T, int nh, int nkv, int page_size, int num_pages,
                               int window, int chunk, float scale, const float* sink, const float* gate, long long gate_ld,
-                              int gate_dv, void* stream) {
+                              int gate_dv, const float* dist, int keep_first, void* stream) {
     if (n_items <= 0) return 0;
     if (!bw_attention_tc_supported(nh, nkv, page_size) || !(scale > 0.f)) return BW_ERR_UNSUPPORTED;
     if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return BW_ERR_UNSUPPORTED;
@@ -442,6 +471,7 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
     if (gate && gate_dv < 0 ? (-gate_dv > HD || gate_ld < (long long)nh)
                             : gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;
     p.gate = gate; p.gate_ld = gate_ld; p.gate_dv = gate_dv;
+    p.dist = dist; p.keep_first = (keep_first > 0 && p.window > 0) ? keep_first : 0;
     bw::launch((attn_tc_kernel), dim3((unsigned)n_items * nkv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, tq, tk, tv, p);
     BW_LAUNCH_CHECK();
     return 0;

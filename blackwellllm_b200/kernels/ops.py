@@ -954,8 +954,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
     if hd > 256:
         raise KernelError(f"attention: the tensor-core kernels are built for head sizes up to 256, got {hd}")
     # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
-    # (a distance bias or kept first keys: the mma.sync kernels)
-    use_tc = attention_tc_supports(hd, G, page_size) and dist is None and not keep_first
+    use_tc = attention_tc_supports(hd, G, page_size)
     rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices, merge_max = attention_work(
         batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64, page_size=page_size, chunk=chunk, keep_first=keep_first)
     part_o = part_ml = None
@@ -968,7 +967,8 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
         tc = _fn("attention_tc", "bw_attention_tc", _ATTN_TC_ARGS, macros=attention_tc_macros(hd))
         _check(tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
                   _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, q.shape[0],
-                  nh, nkv, page_size, num_pages, int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _ptr(g), g_ld, g_dv, _stream()), "attention_tc")
+                  nh, nkv, page_size, num_pages, int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _ptr(g), g_ld, g_dv,
+                  _ptr(dist), keep_first, _stream()), "attention_tc")
         n_rows = 0
         if not n_keys:
             return out
@@ -985,7 +985,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
 
 
 _ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                  c_void_p, c_ll, c_int, c_void_p]
+                                  c_void_p, c_ll, c_int, c_void_p, c_int, c_void_p]
 
 
 def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:

@@ -164,7 +164,8 @@ def _biased_attention(q, k, v, sink, scale, r1, r2, window, keep, gate=None):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,page,window,keep", [(4, 2, 48, 8, 40, 6), (2, 2, 64, 16, 100, 70), (8, 2, 128, 16, 33, 1),
                                                         (6, 3, 96, 16, 64, 64), (3, 1, 16, 32, 7, 20), (4, 1, 32, 16, None, 0),
-                                                        (4, 4, 64, 64, 130, 0), (20, 1, 32, 16, 40, 5)])
+                                                        (4, 4, 64, 64, 130, 0), (20, 1, 32, 16, 40, 5), (4, 1, 256, 16, 70, 130),
+                                                        (16, 4, 128, 16, 128, 64)])
 def test_attention_with_distance_bias_kept_keys_and_head_gate(ops, dtype, nh, nkv, hd, page, window, keep):
     """Prompt portions from position 0 and continued, decode tokens with few and many keys, a two-token portion; the
     window's and the kept keys' edges fall inside tiles and pages."""
