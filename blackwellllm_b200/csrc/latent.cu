@@ -193,11 +193,16 @@ headwise_mma_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const bf1
         const int t = t0 + warp * 16 + (lane >> 2) + 8 * half;
         if (t >= T) continue;
         bf16* dst = y + (size_t)t * ldy + (size_t)h * y_hs;
+        const bool pairs = ((reinterpret_cast<uintptr_t>(dst) & 3) == 0);   // (o is even: a pair of results is one 4-byte store)
 #pragma unroll
         for (int j = 0; j < MO / 8; ++j) {
             const int o = o0 + j * 8 + 2 * (lane & 3);
-            if (o < n_out) dst[o] = __float2bfloat16_rn(acc[j][2 * half]);
-            if (o + 1 < n_out) dst[o + 1] = __float2bfloat16_rn(acc[j][2 * half + 1]);
+            if (pairs && o + 1 < n_out) {
+                *reinterpret_cast<uint32_t*>(dst + o) = bw::pack_bf16x2(acc[j][2 * half], acc[j][2 * half + 1]);
+            } else {
+                if (o < n_out) dst[o] = __float2bfloat16_rn(acc[j][2 * half]);
+                if (o + 1 < n_out) dst[o + 1] = __float2bfloat16_rn(acc[j][2 * half + 1]);
+            }
         }
     }
 }

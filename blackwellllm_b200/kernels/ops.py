@@ -217,11 +217,13 @@ def discard_pending(t: Optional[torch.Tensor] = None) -> None:
 
 
 def gemm_tc_planes(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                   force_splits: int = 0) -> torch.Tensor:
+                   force_splits: int = 0, after: int = 0) -> torch.Tensor:
     """x @ w.T (+ bias) for up to GEMM_PLANES_MAX_TOKENS tokens as float32 planes [S, M, N] that
     add up to it (in plane order; the bias is in plane 0), in this module's plane buffer: valid until
-    the next call.  An outstanding sum is resolved first."""
-    resolve_pending()
+    the next call.  An outstanding sum is resolved first, unless ``after`` > 0: then the planes start that many
+    floats into the buffer and what lies before them stays (:func:`gemm_tc_deferred` chains two sums so)."""
+    if not after:
+        resolve_pending()
     _dev(x, "x", torch.bfloat16, contiguous=False); _dev(w, "w", torch.bfloat16)
     M, K = x.shape
     N = w.shape[0]
@@ -232,7 +234,7 @@ def gemm_tc_planes(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
         _dev(bias, "bias")
         if bias.numel() != N:
             raise KernelError("gemm: bias must have N entries")
-    buf = _plane_buffer(x.device)
+    buf = _plane_buffer(x.device)[after:]
     n = c_int(0)
     fn = _fn("gemm_tc", "bw_gemm_tc_planes", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int,
                                                c_ll, c_int, ctypes.POINTER(c_int), c_void_p],
@@ -256,6 +258,16 @@ def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     global _pending
     if out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (x.shape[0], w.shape[0]):
         raise KernelError("gemm_tc_deferred: out must be contiguous float32 [M, N]")
+    if (_pending is not None and not overwrite and _pending[0].data_ptr() == out.data_ptr() and _pending[0].shape == out.shape
+            and _pending[1].numel() % 64 == 0 and _pending[1].numel() * 4 <= PLANE_BUFFER_ELEMS
+            and _pending[1].data_ptr() == _plane_buffer(x.device).data_ptr()):
+        # a second sum into the same tensor (a block whose two sublayers both add to the stream): its planes go
+        # behind the first's, and the reader adds them all in one pass, in plane order
+        target, first, ow = _pending
+        more = gemm_tc_planes(x, w, bias, after=first.numel())
+        both = _plane_buffer(x.device)[:first.numel() + more.numel()].view(first.shape[0] + more.shape[0], *first.shape[1:])
+        _pending = (target, both, ow)
+        return
     planes = gemm_tc_planes(x, w, bias)
     _pending = (out, planes, bool(overwrite))
 
@@ -1183,10 +1195,20 @@ def rmsnorm_shift(x: torch.Tensor, gain: torch.Tensor, shift: torch.Tensor, stat
     T, H = x.shape
     if gain.numel() != H or shift.numel() != H or state.dim() != 2 or state.shape[1] != H or T != batch.T:
         raise KernelError("rmsnorm_shift: gain and shift [H], state [slots, H], one row of x per token of the batch")
+    # an outstanding sum into x: in a step of single tokens (no row reads its neighbour) the kernel adds it while it
+    # norms; else a kernel of its own does first
+    global _pending
+    planes = None
+    if (_pending is not None and _pending[0].data_ptr() == x.data_ptr() and _pending[0].shape == x.shape
+            and not _pending[2] and batch.T == batch.R):
+        planes, _pending = _pending[1], None
+    else:
+        resolve_pending()
     h = torch.empty((T, H), dtype=out_dtype, device=x.device) if want_h else None
     hs = torch.empty((T, H), dtype=out_dtype, device=x.device)
-    fn = _fn("rowstate", "bw_rmsnorm_shift", [c_void_p] * 10 + [c_int, c_int, c_int, c_float, c_void_p])
-    _check(fn(_ptr(x), _ptr(gain), _ptr(shift), _ptr(state), _ptr(batch.positions), _ptr(batch.req_of_token),
+    fn = _fn("rowstate", "bw_rmsnorm_shift", [c_void_p, c_void_p, c_int, c_ll] + [c_void_p] * 9 + [c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(x), _ptr(planes), 0 if planes is None else planes.shape[0], 0 if planes is None else planes.stride(0),
+              _ptr(gain), _ptr(shift), _ptr(state), _ptr(batch.positions), _ptr(batch.req_of_token),
               _ptr(batch.cu_q), _ptr(batch.state_slot), _ptr(h), _ptr(hs), _code(hs, "out"), T, H, float(eps), _stream()),
            "rmsnorm_shift")
     return h, hs

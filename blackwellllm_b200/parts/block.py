@@ -191,8 +191,9 @@ class ParallelBlock(PreNormBlock):
     """ONE norm whose output both sublayers read: ``h = norm(x)``, ``x += mixer(h') + ffn(h)``.  With the layer's
     ``token_shift`` (a vector s), the mixer reads ``h'_t = h_t + (h_{t-1} - h_t) * s`` (zeros before a sequence's first
     token) and the feed-forward h_t as it is; norm and shift are one kernel, and h of a request's last token is kept in a
-    state slot of the block's own between steps (every run of the block has its own)."""
-    takes_pending = False
+    state slot of the block's own between steps (every run of the block has its own).  The two sublayers' sums into the
+    stream may stay open together (``ops.gemm_tc_deferred`` chains them); the next block's norm adds them."""
+    takes_pending = True
 
     def __init__(self, layer_spec, hidden_size: int, ctx: BuildContext):
         self.spec = layer_spec
@@ -237,7 +238,6 @@ class ParallelBlock(PreNormBlock):
             else (FixedStateRequest((self.hidden_size,), torch.float32),)
 
     def forward(self, residual, batch, cache, owns_cache: bool = True) -> None:
-        ops.resolve_pending()
         if self.shift_name is not None:
             if not owns_cache:
                 raise ops.KernelError("a block with a token shift owns its state: it cannot run on another run's cache")
@@ -246,7 +246,7 @@ class ParallelBlock(PreNormBlock):
                                       self.mixer_norm.eps, self.ctx.dtype, want_h=self.ffn is not None)
         else:
             mixer_cache = cache
-            h = hs = self.mixer_norm.forward(residual)
+            h = hs = self._normed(self.mixer_norm, residual)
         self.mixer.forward(hs, residual, batch, mixer_cache, owns_cache)
         if self.ffn is not None:
             self.ffn.forward(h, residual, batch)

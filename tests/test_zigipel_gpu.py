@@ -74,7 +74,7 @@ def test_hashed_second_table_across_steps(ops, dtype, H, buckets, mp, mc):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H", [64, 50, 328])
+@pytest.mark.parametrize("H", [64, 50, 328, 2052, 4096])
 def test_norm_and_token_shift_across_steps(ops, out_dtype, H):
     eps = 1e-5
     gain, shift = 1.0 + rnd(H, seed=1, scale=0.3), torch.rand(H, generator=torch.Generator().manual_seed(2))
@@ -108,11 +108,48 @@ def test_norm_and_token_shift_across_steps(ops, out_dtype, H):
         assert torch.equal(whole, torch.cat(got_s[2]).float())
 
 
+@pytest.mark.parametrize("T,n_req", [(3, 3), (1, 1), (6, 2), (40, 40)])
+def test_two_open_sums_into_the_stream_are_added_by_the_next_norm(ops, T, n_req):
+    """Two products of a few tokens into the same float32 stream stay open together; the norm-and-shift kernel adds them
+    in a step of single tokens (and leaves the stream summed), a kernel of its own does otherwise; either way the stream
+    and both outputs are those of the sums made one after the other."""
+    from blackwellllm_b200.parts.linear import Linear
+    H, K1, K2, eps = 256, 512, 1024, 1e-5
+    gain, shift = 1.0 + rnd(H, seed=1, scale=0.3), torch.rand(H, generator=torch.Generator().manual_seed(2))
+    x = rnd(T, H, seed=3)
+    a1, a2 = rnd(T, K1, seed=4).bfloat16(), rnd(T, K2, seed=5).bfloat16()
+    w1, w2 = rnd(H, K1, seed=6, scale=0.05).bfloat16(), rnd(H, K2, seed=7, scale=0.05).bfloat16()
+    b2 = rnd(H, seed=8).bfloat16()
+    per = T // n_req
+    batch = Rows([per] * n_req, [5 * (r + 1) for r in range(n_req)], list(range(n_req)))
+    state0 = rnd(n_req, H, seed=9)
+    stream, state = d(x), d(state0)
+    ops.discard_pending()
+    Linear(d(w1)).add_to(d(a1), stream)
+    Linear(d(w2), d(b2)).add_to(d(a2), stream)
+    assert ops.pending_target() is stream
+    h, hs = ops.rmsnorm_shift(stream, d(gain), d(shift), state, batch, eps, torch.float32)
+    assert ops.pending_target() is None
+    total = x.double() + a1.double() @ w1.double().T + a2.double() @ w2.double().T + b2.double()
+    assert float((stream.cpu().double() - total).abs().max()) <= 2e-5 * float(total.abs().max())
+    want_h = plain.rms_norm(total, gain.double(), eps)
+    assert float((h.cpu().double() - want_h).abs().max()) <= 1e-4 * float(want_h.abs().max())
+    for r in range(n_req):
+        rows = slice(r * per, (r + 1) * per)
+        before = torch.cat([state0[r:r + 1].double(), want_h[rows][:-1]])
+        want_s = want_h[rows] + (before - want_h[rows]) * shift.double()
+        assert float((hs[rows].cpu().double() - want_s).abs().max()) <= 1e-4 * float(want_h.abs().max())
+        assert float((state[r].cpu().double() - want_h[rows][-1]).abs().max()) <= 1e-4 * float(want_h.abs().max())
+    assert ops.gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_two_streams_side_by_side_and_gated_gelu(ops, dtype):
     a, b = rnd(7, 50, seed=1), rnd(7, 50, seed=2)
     out = ops.concat2_cast(d(a), d(b), dtype).cpu()
     assert torch.equal(out, torch.cat([a, b], dim=1).to(dtype))
+    a, b = rnd(5, 2052, seed=1), rnd(5, 2052, seed=2)
+    assert torch.equal(ops.concat2_cast(d(a), d(b), dtype).cpu(), torch.cat([a, b], dim=1).to(dtype))
     gu = rnd(9, 2 * 40, seed=3, scale=2.0)
     got = ops.glu(d(gu), ops.ACT_GELU_TANH, out_dtype=dtype).cpu().double()
     want = plain.gelu_tanh(gu[:, :40].double()) * gu[:, 40:].double()
