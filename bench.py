@@ -366,7 +366,7 @@ def _zigipel_shape(width, heads, kv, hd, window, keep, l_heads, l_dim, l_rot, l_
     mlp = {"kind": "dense", "ff": ff}
     layers = [{"type": "attention", "mixer": att, "mlp": mlp}, {"type": "latent_attention", "mixer": lat, "mlp": mlp}] * pairs
     design = {"architecture": "Zigipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
-              "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+              "embedding": {"bigram": {"buckets": 65521, "mul_prev": 37, "mul_cur": 11}},
               "loop": {"start": 0, "stop": 2 * pairs, "times": times}, "layers": layers}
     dense = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": width,
              "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd, "intermediate_size": ff,

@@ -199,7 +199,7 @@ def _biased_attention(q, k, v, sink, scale, r1, r2, window, keep, gate=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd,page,window,keep", [(4, 2, 48, 8, 40, 6), (2, 2, 64, 16, 100, 70), (8, 2, 128, 16, 33, 1),
+@pytest.mark.parametrize("nh,nkv,hd,page,window,keep", [(4, 2, 80, 8, 44, 7), (2, 2, 64, 16, 100, 70), (8, 2, 128, 16, 33, 1),
                                                         (6, 3, 96, 16, 64, 64), (3, 1, 16, 32, 7, 20), (4, 1, 32, 16, None, 0),
                                                         (4, 4, 64, 64, 130, 0), (20, 1, 32, 16, 40, 5), (4, 1, 256, 16, 70, 130),
                                                         (16, 4, 128, 16, 128, 64)])
@@ -238,13 +238,13 @@ def test_attention_with_distance_bias_kept_keys_and_head_gate(ops, dtype, nh, nk
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hd", [48, 64])
+@pytest.mark.parametrize("hd", [80, 64])
 @pytest.mark.parametrize("q_len", [1, 2, 50])
 def test_one_loud_key_at_the_edges_of_window_and_kept_keys(ops, dtype, hd, q_len):
     """All scores of the last query are 0 but one key's.  Just inside the window or among the kept first keys the row
     returns that key's value; just outside either it returns the mean of the others; hundreds of positions back."""
     from test_kernels_gpu import FakeBatch, paged_case
-    nh, nkv, page, window, keep = 4, 2, 16, 40, 6
+    nh, nkv, page, window, keep = 4, 2, 16, 36, 5
     L = 700
     last = L - 1
     for loud, seen in [(last - window + 1, True), (last - window, False), (keep - 1, True), (keep, False), (0, True),
