@@ -323,6 +323,29 @@ __device__ __forceinline__ void rope_direct(const Epilogue& ep, const uint32_t (
     }
 }
 
+// The biases of the 32 features f0 .. f0 + 31 (f0 a multiple of 32; the same for every lane), zeros from feature
+// `limit` on: 16-byte loads where the address and the limit allow them.
+__device__ __forceinline__ void load_bias32(const Epilogue& ep, int f0, int limit, float (&b)[32]) {
+    const bool whole = f0 + 32 <= limit && (((uintptr_t)ep.bias) & 15) == 0;
+    if (whole && ep.bias_type == BW_F32) {
+        const float4* src = reinterpret_cast<const float4*>((const float*)ep.bias + f0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float4 t = __ldg(src + i); b[4 * i] = t.x; b[4 * i + 1] = t.y; b[4 * i + 2] = t.z; b[4 * i + 3] = t.w; }
+    } else if (whole) {
+        const uint4* src = reinterpret_cast<const uint4*>((const bf16*)ep.bias + f0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 t = __ldg(src + i);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { b[8 * i + 2 * k] = __uint_as_float(w[k] << 16); b[8 * i + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) b[i] = f0 + i < limit ? bias_at(ep, f0 + i) : 0.f;
+    }
+}
+
 // SwiGLU epilogue in the normal orientation: the thread holds 32 consecutive features f0 .. f0 + 31 of
 // ONE token, f0 a multiple of 32: 16 gate sums, then the 16 up sums of the same output features.
 // It writes silu(gate) * up for those 16 features as 32 contiguous bytes.
@@ -593,6 +616,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         uint8_t* box = (uint8_t*)staging + ((warp - 2) * 2 + (chunk & 1)) * 4096;
                         if (lane == 0) bw::bulk_wait_group_read<1>();   // the box used two chunks ago has been read
                         __syncwarp();
+                        if (ep.bias) {
+                            float b[32];
+                            load_bias32(ep, tile_b * BN + c0, b_rows, b);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + b[i]);
+                        }
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             uint4 q4;
@@ -863,6 +892,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         uint8_t* box = (uint8_t*)staging + ((warp - 2) * 2 + (chunk & 1)) * 4096;
                         if (lane == 0) bw::bulk_wait_group_read<1>();
                         __syncwarp();
+                        if (ep.bias) {
+                            float b[32];
+                            load_bias32(ep, tile_b * BN + c0, b_rows, b);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + b[i]);
+                        }
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {   // columns past this tile's width go out as zeros
                             const bool in = c0 + 4 * j < BN;   // BN is a multiple of 16: whole groups of four
@@ -1243,7 +1278,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     CUtensorMap tc;
     std::memset(&tc, 0, sizeof(tc));
     ep.tma_add = 0;
-    if (!tr && accumulate && !bias && splits == 1 && !rope && !swiglu && ((uintptr_t)out & 15) == 0 && ldo % 4 == 0) {
+    if (!tr && accumulate && splits == 1 && !rope && !swiglu && ((uintptr_t)out & 15) == 0 && ldo % 4 == 0) {
         if (!make_out_map(&tc, out, M, N, ldo)) return BW_ERR_DRIVER;
         ep.tma_add = 1;
     }

@@ -1190,20 +1190,20 @@ def rmsnorm_shift(x: torch.Tensor, gain: torch.Tensor, shift: torch.Tensor, stat
     """(h, hs): ``h = x / rms(x) * gain`` and ``hs_t = h_t + (h_{t-1} - h_t) * shift`` with zeros before a sequence's
     first token.  ``state`` (float32 [slots, H]) holds h of every request's last token so far: a portion's first token
     reads it, and it takes the portion's last h.  ``want_h=False``: only hs is written (h is None)."""
+    # an outstanding sum into x: in a step of single tokens (no row reads its neighbour) the kernel adds it while it
+    # norms; else a kernel of its own does first (the check of x below would ask for it)
+    global _pending
+    planes = None
+    if (_pending is not None and _pending[0].data_ptr() == x.data_ptr() and _pending[0].shape == x.shape
+            and not _pending[2] and batch.T == batch.R and x.dim() == 2 and x.shape[0] == batch.T):
+        planes, _pending = _pending[1], None
+    else:
+        resolve_pending()
     _dev(x, "x", torch.float32); _dev(gain, "gain", torch.float32); _dev(shift, "shift", torch.float32)
     _dev(state, "state", torch.float32)
     T, H = x.shape
     if gain.numel() != H or shift.numel() != H or state.dim() != 2 or state.shape[1] != H or T != batch.T:
         raise KernelError("rmsnorm_shift: gain and shift [H], state [slots, H], one row of x per token of the batch")
-    # an outstanding sum into x: in a step of single tokens (no row reads its neighbour) the kernel adds it while it
-    # norms; else a kernel of its own does first
-    global _pending
-    planes = None
-    if (_pending is not None and _pending[0].data_ptr() == x.data_ptr() and _pending[0].shape == x.shape
-            and not _pending[2] and batch.T == batch.R):
-        planes, _pending = _pending[1], None
-    else:
-        resolve_pending()
     h = torch.empty((T, H), dtype=out_dtype, device=x.device) if want_h else None
     hs = torch.empty((T, H), dtype=out_dtype, device=x.device)
     fn = _fn("rowstate", "bw_rmsnorm_shift", [c_void_p, c_void_p, c_int, c_ll] + [c_void_p] * 9 + [c_int, c_int, c_int, c_float, c_void_p])

@@ -318,6 +318,24 @@ def test_values_are_cached_with_unit_root_mean_square(ops, out_dtype, nh, nkv, d
         assert float(k_row[:, dq:].abs().sum()) == 0.0 and float(v_row[:, dv:].abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,n_in,n_out", [(1, 3, 40, 24), (70, 2, 64, 64), (130, 4, 128, 192), (65, 2, 192, 128), (9, 1, 256, 72),
+                                            (100, 2, 320, 40), (33, 1, 520, 130), (64, 3, 24, 200)])
+def test_a_product_per_head_on_the_tensor_cores(ops, x_dtype, T, H, n_in, n_out):
+    """y[t, h] = W_h x[t, h] with bfloat16 weights: inner sizes below, at and above what one round of staging takes, rows
+    with other columns around the heads' inputs and outputs."""
+    x_hs, y_hs = n_in + 8, n_out + 16
+    x = rnd(T, 16 + H * x_hs, seed=1).to(x_dtype)
+    w = rnd(H, n_out, n_in, seed=2, scale=n_in ** -0.5).bfloat16()
+    y = torch.full((T, 8 + H * y_hs), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.headwise_linear(d(x), 16, x_hs, d(w), y, 8, y_hs)
+    xin = x[:, 16:].view(T, H, x_hs)[:, :, :n_in].bfloat16().double()      # float32 inputs are rounded on the way
+    want = torch.einsum("thi,hoi->tho", xin, w.double())
+    got = y.cpu().double()[:, 8:].view(T, H, y_hs)
+    assert float((got[:, :, :n_out] - want).abs().max()) <= 1e-2 * float(want.abs().max())
+    assert torch.all(got[:, :, n_out:] == 7.0) and torch.all(y.cpu()[:, :8] == 7.0)      # nothing beside the outputs is touched
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,d_,dr,dv,rank,page,window", [(2, 16, 8, 24, 40, 8, 9), (3, 8, 16, 8, 24, 16, 30), (4, 32, 32, 48, 96, 16, None),
                                                          (20, 12, 12, 20, 24, 32, 50), (2, 16, 16, 24, 272, 16, 40), (17, 8, 8, 8, 24, 8, 20)])
