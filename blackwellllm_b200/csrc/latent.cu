@@ -109,11 +109,9 @@ headwise_linear_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const 
 
 // The same product on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 sums) for bfloat16 weights and
 // results: a CTA of 4 warps makes 64 tokens x 64 outputs of one head, warp w the tokens 16 w .. 16 w + 15; the operands
-// pass through shared memory `kc` inner values at a time, kc = all of them up to 256 (one round of loads, all in flight
-// at once, and one barrier; float32 inputs are rounded to bfloat16 on the way; 16-byte loads where sizes and addresses
-// allow them: `vec`), rows padded by 16 bytes so that the 8 rows of an ldmatrix fall into different banks.
-constexpr int MT = 64, MO = 64, MK_MAX = 256;
-__host__ __device__ inline int headwise_chunk(int n_in) { const int r = (n_in + 63) / 64 * 64; return r < MK_MAX ? r : MK_MAX; }
+// pass through shared memory 64 inner values at a time (float32 inputs are rounded to bfloat16 on the way; 16-byte
+// loads where sizes and addresses allow them: `vec`), rows padded to 144 bytes so that the 8 rows of an ldmatrix fall into different banks.
+constexpr int MT = 64, MO = 64, MK = 64, MROW = (MK + 8) * 2;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
@@ -130,26 +128,24 @@ headwise_mma_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const bf1
                     long long ldy, int y_hs, int T, int n_in, int n_out, int vec) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
-    extern __shared__ __align__(16) uint8_t hw_smem[];
-    const int MK = headwise_chunk(n_in), MROW = (MK + 8) * 2, hk = MK / 2;
-    uint8_t* xs = hw_smem;                 // [MT][MROW]
-    uint8_t* ws = hw_smem + MT * MROW;     // [MO][MROW]
+    __shared__ __align__(16) uint8_t xs[MT * MROW];
+    __shared__ __align__(16) uint8_t ws[MO * MROW];
     const int h = blockIdx.z, t0 = blockIdx.x * MT, o0 = blockIdx.y * MO;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bf16* wh = w + (size_t)h * n_out * n_in;
     float acc[MO / 8][4];
 #pragma unroll
     for (int j = 0; j < MO / 8; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-    // every thread stages half a row (MK / 2 inner values) of each operand, 8 at a time
-    const int srow = threadIdx.x >> 1, scol = (threadIdx.x & 1) * hk;
+    // every thread stages 32 inner values of one row of each operand, 8 at a time
+    const int srow = threadIdx.x >> 1, scol = (threadIdx.x & 1) * 32;
     for (int k0 = 0; k0 < n_in; k0 += MK) {
         const int t = t0 + srow, o = o0 + srow;
         const XT* src = x + (size_t)(t < T ? t : 0) * ldx + (size_t)h * x_hs + k0 + scol;
         const bf16* wsrc = wh + (size_t)(o < n_out ? o : 0) * n_in + k0 + scol;
         uint8_t* dst = xs + srow * MROW + scol * 2;
         uint8_t* wdst = ws + srow * MROW + scol * 2;
-#pragma unroll 4
-        for (int c = 0; c < hk; c += 8) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
             const bool in = k0 + scol + c < n_in;      // (vec: n_in is a multiple of 8, so a chunk is inside or outside)
             uint4 xv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
             if (vec) {
@@ -177,7 +173,7 @@ headwise_mma_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const bf1
             *reinterpret_cast<uint4*>(wdst + c * 2) = wv;
         }
         __syncthreads();
-#pragma unroll 4
+#pragma unroll
         for (int ks = 0; ks < MK / 16; ++ks) {
             uint32_t a[4];
             ldsm_x4(smem_addr(xs) + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * MROW + 16 * (lane >> 4) + ks * 32,
@@ -253,18 +249,11 @@ BW_EXPORT int bw_headwise_linear(const void* x, int x_type, long long ldx, int x
     // 16-byte loads: 8 inner values of a row at a time, every row starting on a 16-byte boundary
     const int xe = x_type == BW_F32 ? 4 : 8;      // elements of x in 16 bytes
     const int vec = n_in % 8 == 0 && ldx % xe == 0 && x_hs % xe == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
-    const size_t msmem = (size_t)(MT + MO) * (headwise_chunk(n_in) + 8) * 2;   // up to 67,584 bytes: above the default limit
-    if (w_type == BW_BF16 && y_type == BW_BF16) {
-        static bool raised_f[bw::MAX_DEVICES] = {}, raised_b[bw::MAX_DEVICES] = {};
-        const size_t most = (size_t)(MT + MO) * (MK_MAX + 8) * 2;
-        if (x_type == BW_F32 && bw::allow_dynamic_smem(headwise_mma_kernel<float>, most, raised_f) != cudaSuccess) return BW_ERR_DRIVER;
-        if (x_type == BW_BF16 && bw::allow_dynamic_smem(headwise_mma_kernel<bf16>, most, raised_b) != cudaSuccess) return BW_ERR_DRIVER;
-    }
     if (x_type == BW_F32 && w_type == BW_F32 && y_type == BW_F32) BW_HW(float, float, float);
     else if (x_type == BW_F32 && w_type == BW_BF16 && y_type == BW_BF16)      // bfloat16 weights and results: the tensor cores
-        bw::launch((headwise_mma_kernel<float>), mgrid, dim3(128), msmem, s, (const float*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec);
+        bw::launch((headwise_mma_kernel<float>), mgrid, dim3(128), 0, s, (const float*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec);
     else if (x_type == BW_BF16 && w_type == BW_BF16 && y_type == BW_BF16)
-        bw::launch((headwise_mma_kernel<bf16>), mgrid, dim3(128), msmem, s, (const bf16*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec);
+        bw::launch((headwise_mma_kernel<bf16>), mgrid, dim3(128), 0, s, (const bf16*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec);
     else return BW_ERR_UNSUPPORTED;
 #undef BW_HW
     BW_LAUNCH_CHECK();

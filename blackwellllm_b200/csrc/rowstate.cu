@@ -97,7 +97,7 @@ template <int W> __device__ __forceinline__ float sum_squares(const float* __res
 // a matrix product that its kernel left unsummed; x[t] += planes[0][t] + planes[1][t] + ... first, written back.  Every
 // thread re-reads only what it wrote itself.
 template <typename OT, int W>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rmsnorm_shift_kernel(float* __restrict__ x, const float* __restrict__ planes, int n_planes, size_t plane_stride,
                      const float* __restrict__ gain, const float* __restrict__ shift,
                      float* __restrict__ state, const int* __restrict__ positions, const int* __restrict__ req_of_token,
@@ -117,10 +117,10 @@ rmsnorm_shift_kernel(float* __restrict__ x, const float* __restrict__ planes, in
         for (int c = threadIdx.x * W; c < H; c += blockDim.x * W) {
             float v[W];
             ld<W>(xr + c, v);
-            for (int p0 = 0; p0 < n_planes; p0 += 4) {   // in plane order, four loads in flight at a time
-                float a[4][W];
+            for (int p0 = 0; p0 < n_planes; p0 += 8) {   // in plane order, eight loads in flight at a time
+                float a[8][W];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
+                for (int k = 0; k < 8; ++k) {
                     if (p0 + k < n_planes) ld<W>(pr + (size_t)(p0 + k) * plane_stride + c, a[k]);
                     else {
 #pragma unroll
@@ -128,7 +128,7 @@ rmsnorm_shift_kernel(float* __restrict__ x, const float* __restrict__ planes, in
                     }
                 }
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
+                for (int k = 0; k < 8; ++k)
 #pragma unroll
                     for (int j = 0; j < W; ++j) v[j] += a[k][j];
             }
@@ -230,7 +230,10 @@ BW_EXPORT int bw_rmsnorm_shift(float* x, const float* planes, int n_planes, long
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = H % 4 == 0 && aligned16(x) && aligned16(gain) && aligned16(shift) && aligned16(state) && aligned16(hs_out) &&
                      aligned16(h_out) && (!planes || (aligned16(planes) && plane_stride % 4 == 0));
-    const int threads = H >= 1024 ? 256 : 128;
+    // with planes (a few rows): a thread per four elements, up to 1,024, so that the loads of the stream and of the
+    // planes are in flight at once
+    int threads = H >= 1024 ? 256 : 128;
+    if (planes) { const int quads = (H / (vec ? 4 : 1) + 31) / 32 * 32; threads = quads > 1024 ? 1024 : (quads < 128 ? 128 : quads); }
 #define BW_RS(OT, W) bw::launch((rmsnorm_shift_kernel<OT, W>), dim3(T), dim3(threads), 0, s, x, planes, n_planes, (size_t)plane_stride, \
                                 gain, shift, state, positions, req_of_token, cu_q, state_slot, (OT*)h_out, (OT*)hs_out, H, eps)
     if (out_type == BW_F32) { if (vec) BW_RS(float, 4); else BW_RS(float, 1); }
