@@ -343,6 +343,37 @@ def test_latent_attention_mixer_alone(ops, dtype, H, d_, dr, dv, rank, page, win
     """The mixer part against the plain function: a prompt in two portions and then single tokens, next to another
     request; the cache holds one row of rank + rot_dim channels per token (one plane); 20 heads share it (two groups of 10 on the tensor cores) or 17 (one call); a latent
     row wider than the tensor-core kernels' head sizes."""
+    _latent_mixer_case(ops, dtype, H, d_, dr, dv, rank, page, window)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,d_,dr,dv,rank,page,window", [(2, 16, 16, 24, 40, 8, 9), (3, 8, 32, 8, 24, 16, 30), (4, 64, 64, 32, 64, 16, 17)])
+def test_latent_attention_loud_keys_at_the_windows_edge(ops, dtype, H, d_, dr, dv, rank, page, window):
+    """Three tokens whose rotated key part is many times the others': each lies just inside the window of one query (the
+    last of a prompt portion, one in its middle, a decoded one) and just outside the next query's.  Their sign is chosen so
+    that the plain result of the query that still sees them changes greatly when the window is one key shorter; the mixer
+    must then agree with the plain result at the true window."""
+    def loud(xs, t, m, eps):
+        x = xs[0]
+        for i in (62, 50, 74):          # the queries: last of the second portion, inside it, the last decoded token
+            j = i - window + 1
+            best = None
+            for sign in (8.0, -8.0):
+                y = x.clone()
+                y[j] = x[j] * sign
+                tt = {k: v.double() for k, v in t.items()}
+                full = plain.latent_attention(y.double(), tt, m, eps)[i]
+                short = plain.latent_attention(y.double(), tt, dict(m, mask={"size": window - 1}), eps)[i]
+                gap = float((full - short).abs().max()) / float(full.abs().max())
+                if best is None or gap > best[0]:
+                    best = (gap, y)
+            assert best[0] > 0.2, (i, best[0])      # the edge key decides the row
+            x = best[1]
+        xs[0] = x
+    _latent_mixer_case(ops, dtype, H, d_, dr, dv, rank, page, window, edit=loud)
+
+
+def _latent_mixer_case(ops, dtype, H, d_, dr, dv, rank, page, window, edit=None):
     from blackwellllm_b200.config.specs import LatentAttentionSpec, RopeSpec, YarnRopeScaling
     from blackwellllm_b200.parts import BuildContext, build_mixer
     from test_kernels_gpu import FakeBatch
@@ -362,6 +393,8 @@ def test_latent_attention_mixer_alone(ops, dtype, H, d_, dr, dv, rank, page, win
     m = {"heads": H, "dim": d_, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "scale": 0.2, "rot": rot}
     if window:
         m["mask"] = {"size": window}
+    if edit is not None:
+        edit(xs, t, m, eps)
     want = {r: plain.latent_attention(x.double(), {k: v.double() for k, v in t.items()}, m, eps) for r, x in xs.items()}
     n_pages = -(-L // page) + -(-30 // page)
     pool = torch.full((1, n_pages, 1, page, rq.head_dim), float("nan"), dtype=dtype, device=DEV)
