@@ -352,13 +352,16 @@ def test_latent_attention_loud_keys_at_the_windows_edge(ops, dtype, H, d_, dr, d
     """Three tokens whose rotated key part is many times the others': each lies just inside the window of one query (the
     last of a prompt portion, one in its middle, a decoded one) and just outside the next query's.  Their sign is chosen so
     that the plain result of the query that still sees them changes greatly when the window is one key shorter; the mixer
-    must then agree with the plain result at the true window."""
+    must then agree with the plain result at the true window.  (bfloat16: keys three times the others' instead of eight
+    times, and a wider bound: the rounding of a score grows with the score.)"""
+    factor = 8.0 if dtype == torch.float32 else 3.0
+
     def loud(xs, t, m, eps):
         x = xs[0]
         for i in (62, 50, 74):          # the queries: last of the second portion, inside it, the last decoded token
             j = i - window + 1
             best = None
-            for sign in (8.0, -8.0):
+            for sign in (factor, -factor):
                 y = x.clone()
                 y[j] = x[j] * sign
                 tt = {k: v.double() for k, v in t.items()}
@@ -370,10 +373,10 @@ def test_latent_attention_loud_keys_at_the_windows_edge(ops, dtype, H, d_, dr, d
             assert best[0] > 0.2, (i, best[0])      # the edge key decides the row
             x = best[1]
         xs[0] = x
-    _latent_mixer_case(ops, dtype, H, d_, dr, dv, rank, page, window, edit=loud)
+    _latent_mixer_case(ops, dtype, H, d_, dr, dv, rank, page, window, edit=loud, bf16_tol=5e-2)
 
 
-def _latent_mixer_case(ops, dtype, H, d_, dr, dv, rank, page, window, edit=None):
+def _latent_mixer_case(ops, dtype, H, d_, dr, dv, rank, page, window, edit=None, bf16_tol=3e-2):
     from blackwellllm_b200.config.specs import LatentAttentionSpec, RopeSpec, YarnRopeScaling
     from blackwellllm_b200.parts import BuildContext, build_mixer
     from test_kernels_gpu import FakeBatch
@@ -421,7 +424,7 @@ def _latent_mixer_case(ops, dtype, H, d_, dr, dv, rank, page, window, edit=None)
             got[r].append(res[o:o + n].cpu().double())
             o += n
             at[r] += n
-    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    tol = 2e-5 if dtype == torch.float32 else bf16_tol
     for r in (0, 1):
         g = torch.cat(got[r])
         assert float((g - want[r][:g.shape[0]]).abs().max()) <= tol * float(want[r].abs().max()), r
