@@ -82,15 +82,15 @@ struct Epilogue {
     RopeOut rope;
 };
 
+// The gated activations share one form, g' sigmoid(a) u': silu has a = g; the clamped form clamps g and u first (u' = u + 1)
+// and has a = alpha g'; the tanh form of gelu, 0.5 g (1 + tanh z) = g sigmoid(2 z) with z = sqrt(2 / pi) (g + 0.044715 g^3).
+// One body with selects keeps the unrolled epilogues short.
 __device__ __forceinline__ float ep_glu(const Epilogue& ep, float g, float u) {
-    if (ep.act == BW_ACT_CLAMPED_SWISH) {
-        g = fminf(g, ep.act_limit);
-        u = fminf(fmaxf(u, -ep.act_limit), ep.act_limit) + 1.f;
-        return __fdividef(g, 1.f + __expf(-ep.act_alpha * g)) * u;
-    }
-    if (ep.act == BW_ACT_GELU_TANH)   // 0.5 g (1 + tanh z) = g sigmoid(2 z), z = sqrt(2 / pi) (g + 0.044715 g^3)
-        return __fdividef(g, 1.f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g))) * u;
-    return __fdividef(g, 1.f + __expf(-g)) * u;
+    const bool clamped = ep.act == BW_ACT_CLAMPED_SWISH, gelu = ep.act == BW_ACT_GELU_TANH;
+    const float gc = clamped ? fminf(g, ep.act_limit) : g;
+    const float uc = clamped ? fminf(fmaxf(u, -ep.act_limit), ep.act_limit) + 1.f : u;
+    const float a = gelu ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : (clamped ? ep.act_alpha * gc : g);
+    return __fdividef(gc, 1.f + __expf(-a)) * uc;
 }
 __device__ __forceinline__ float ep_unary(const Epilogue& ep, float v) {
     if (ep.act == BW_ACT_RELU2) { v = fmaxf(v, 0.f); return v * v; }
