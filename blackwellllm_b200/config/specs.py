@@ -126,6 +126,20 @@ class AttentionSpec:
     v_norm_eps: Optional[float] = None
     distance_bias: bool = False
     keep_first: int = 0
+    # ``score_softcap``: the scaled score s becomes cap * tanh(s / cap) before any bias is added.  ``distance_table_far``:
+    # a learned bias per (distance, query head) is added to the score (after the cap; the score scale does not multiply
+    # it): tensor "rel" [rows, heads]; distances below rows / 2 have a row each, larger ones share rows on a logarithmic
+    # scale that reaches the last row at this distance (``kernels.ops.distance_bucket_table``).  ``distance_table_rows``:
+    # the table's rows where the configuration states them (None: whatever the stored tensor has).  ``fixed_sink``: the
+    # softmax's denominator has one more term exp(fixed_sink) that is a constant of the design, not a tensor (0.0: one is
+    # added to the denominator).  ``value_mix``: the name of a number lam (a tensor without axes): in every layer of the
+    # model that has it but the first such layer, the values become (1 - lam) v + lam v_first before they are cached,
+    # v_first being the first such layer's values of the same token (the first layer's own number is not used).
+    score_softcap: Optional[float] = None
+    distance_table_far: Optional[float] = None
+    distance_table_rows: Optional[int] = None
+    fixed_sink: Optional[float] = None
+    value_mix: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -135,7 +149,11 @@ class LatentAttentionSpec:
     ``[W_uk,h c, rotated k_rot]`` and the value ``W_uv,h c``; its query ``W_q,h x`` is laid out as ``head_dim`` plain
     channels, then ``rot_dim`` rotated ones.  Only c and the rotated k_rot are cached.  ``position``: the rotary
     encoding of the rotated parts (its ``rotary_dim`` = ``rot_dim``).  ``window``, ``sink``, ``softmax_scale`` as in
-    :class:`AttentionSpec`.  ``names``: (role, name) pairs for q, dkv, dkv_norm, uk, uv, o, sink."""
+    :class:`AttentionSpec`.  ``names``: (role, name) pairs for q, dkv, dkv_norm, uk, uv, o, sink (and dq, dq_norm, uq, g).
+    ``q_rank``: the queries come through a latent of their own, ``q = W_uq rms_norm(W_dq x) * gain`` (tensors dq
+    [q_rank, hidden], dq_norm [q_rank], uq [heads * (head_dim + rot_dim), q_rank]) instead of one tensor q.
+    ``output_gate``: the concatenated heads' outputs are multiplied element by element by sigmoid(W_g x) (tensor g
+    [heads * v_head_dim, hidden]) before the output projection."""
     num_heads: int
     head_dim: int
     rot_dim: int
@@ -147,6 +165,26 @@ class LatentAttentionSpec:
     window: Optional[int] = None
     sink: bool = False
     kind: str = "latent_attention"
+    names: Tuple[Tuple[str, str], ...] = ()
+    q_rank: Optional[int] = None
+    output_gate: bool = False
+
+
+@dataclass(frozen=True)
+class MatrixLSTMSpec:
+    """A recurrent mixer with a [key_dim, value_dim] matrix memory per head and exponential gates (mLSTM):
+    ``q = W_q x / sqrt(key_dim)``, ``k = W_k x``, ``v = W_v x``; per head a log input gate ``i = cap tanh((w_i x + b_i) /
+    cap)`` and a log forget gate ``f = log_sigmoid(cap tanh((w_f x + b_f) / cap))``; with a running maximum m (from 0):
+    ``m' = max(f + m, i)``, ``S <- exp(f + m - m') S + exp(i - m') k v^T``, n likewise with k alone,
+    ``o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)``; each head's o is divided by its root mean square, the heads side by
+    side are multiplied by a gain of all heads' size and by ``sigmoid(W_g x)``, then projected.  ``names``: (role, name)
+    pairs for q, k, v, g, o, norm, i, i_bias, f, f_bias."""
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    norm_eps: float
+    kind: str = "matrix_lstm"
     names: Tuple[Tuple[str, str], ...] = ()
 
 
@@ -266,6 +304,9 @@ class LayerSpec:
     # the name of a vector s [hidden]; the mixer then reads h_t + (h_{t-1} - h_t) * s (zeros before a sequence's first
     # token; the feed-forward reads h_t as it is), and the block keeps h of a request's last token between steps.
     token_shift: Optional[str] = None
+    # the "parallel" arrangement: the names of two vectors [hidden] ("layer scale"); the mixer's output is multiplied
+    # channel by channel by the first and the feed-forward's by the second before they are added to the stream
+    layer_scale: Optional[Tuple[str, str]] = None
 
 
 @dataclass(frozen=True)

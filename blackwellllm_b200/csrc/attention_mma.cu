@@ -51,6 +51,9 @@ struct Params {
     // the window (0: none).
     const float* dist;
     int keep_first;
+    // softcap > 0: the scaled score s becomes softcap * tanh(s / softcap) before a bias is added.  rel != null: float32
+    // [nh][rel_len], rel[query head][min(i - j, rel_len - 1)] is added to the score of query position i and key position j.
+    float softcap; const float* rel; int rel_len;
     // gate != null: every output channel c < gate_dv of (token, head) is multiplied by sigmoid(gate[token * gate_ld +
     // head * gate_dv + c]) as it is written, channels from gate_dv on become zero (bw::out_gate)
     const float* gate; long long gate_ld; int gate_dv;
@@ -154,6 +157,10 @@ struct RowState {
     int qpos[2], lo[2];    // the rows' own positions and first visible key (qpos < 0: no such row)
     float r1[2], r2[2];    // the rows' heads' distance bias (used when dist != 0)
     int keep, dist;        // keys below `keep` stay visible; dist != 0: the launch has a distance bias
+    int mod;               // != 0: the launch has a soft cap or a table of biases by distance
+    float cap, inv_cap;    // the soft cap (0: none) and its reciprocal
+    const float* rel[2];   // the rows' heads' rows of the table (null: none)
+    int rel_len;
 };
 
 // The tiles a query tile walks when first keys are kept: the tiles that hold kept keys and lie before the first
@@ -181,6 +188,24 @@ __device__ __forceinline__ void scale_and_mask(float (&s)[NK / 8][4], int key_po
                 const bool seen = d >= 0 && (kp >= st.lo[h] || kp < st.keep);
                 const float b = st.r1[h] * __log2f(fmaf(st.r2[h], (float)(d > 0 ? d : 0), 1.f));
                 const float v = seen ? fmaf(s[j][e], scale_log2, -b) : -INFINITY;
+                s[j][e] = v;
+                mx[h] = fmaxf(mx[h], v);
+            }
+        }
+    } else if (st.mod) {   // (uniform over the launch) the score capped, the table's entry added, then powers of two
+        const float scale = scale_log2 * 0.6931471805599453f;
+#pragma unroll
+        for (int j = 0; j < NK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int kp = key_pos0 + j * 8 + 2 * (lane & 3) + (e & 1);
+                const int d = st.qpos[h] - kp;
+                const bool seen = d >= 0 && (kp >= st.lo[h] || kp < st.keep);
+                float v = s[j][e] * scale;
+                if (st.cap > 0.f) v = bw::soft_cap_fast(v, st.cap, st.inv_cap);
+                if (st.rel[h] && seen) v += bw::table_bias(st.rel[h], st.rel_len, d);
+                v = seen ? v * 1.4426950408889634f : -INFINITY;
                 s[j][e] = v;
                 mx[h] = fmaxf(mx[h], v);
             }
@@ -286,11 +311,15 @@ __device__ __forceinline__ void load_q_frags(const uint8_t* q_rows, uint32_t (&q
 __device__ __forceinline__ void init_rows(const Params& p, RowState& st, int row_base, int n_rows, int q_pos0, int g) {
     const int lane = threadIdx.x & 31;
     st.keep = p.keep_first; st.dist = p.dist != nullptr;
+    st.mod = (p.softcap > 0.f || p.rel != nullptr) && !st.dist;
+    st.cap = p.softcap; st.inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f; st.rel_len = p.rel_len;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int row = row_base + (lane >> 2) + 8 * h;
         st.m[h] = -INFINITY; st.l[h] = 0.f;
         st.r1[h] = st.r2[h] = 0.f;
+        st.rel[h] = nullptr;
+        if (row < n_rows && p.rel) st.rel[h] = p.rel + (size_t)(g * p.G + row % p.G) * p.rel_len;
         if (row < n_rows) {
             st.qpos[h] = q_pos0 + row / p.G;
             st.lo[h] = bw::first_visible(st.qpos[h], p.window, p.chunk);
@@ -945,6 +974,7 @@ BW_EXPORT int bw_attention_head_dim() { return HD; }
 // rope_table float32 [tokens][rd] (cosines, then sines); append != 0: key and value also go to the cache.
 // sink: float32 [nh] or null; gate: float32 [tokens, >= nh * gate_dv] with rows gate_ld apart, or null (see Params);
 // gate_dv < 0: one gate number per head (bw::out_gate).  dist: float32 [2][nh] or null; keep_first: see Params.
+// softcap (> 0: on), rel, rel_len: see Params; not together with dist, nor with qkv.
 // qkv only where the TMA key-slice kernel runs (head size a multiple of 64, pages of 8 to 64 tokens);
 // BW_ERR_UNSUPPORTED otherwise, and nothing was launched.
 BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
@@ -954,8 +984,10 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
                                int nkv, int page_size, int num_pages, int window, int chunk, float scale,
                                const float* qkv, int qkv_planes, long long qkv_plane_stride, const float* rope_table,
                                int rd, int append, int merge_max_slices, const float* sink, const float* gate, long long gate_ld,
-                               int gate_dv, const float* dist, int keep_first, void* stream) {
+                               int gate_dv, const float* dist, int keep_first, float softcap, const float* rel, int rel_len,
+                               void* stream) {
     if (nkv <= 0 || nh % nkv != 0) return BW_ERR_BAD_ARG;
+    if ((rel && rel_len <= 0) || ((rel || softcap > 0.f) && (dist || qkv))) return BW_ERR_UNSUPPORTED;
     const int G = nh / nkv;
     if (G > 16) return BW_ERR_UNSUPPORTED;
     const bool tma_keys = HD % 64 == 0 && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
@@ -979,6 +1011,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     p.scale_log2 = scale * 1.4426950408889634f;
     p.sink = sink;
     p.dist = dist; p.keep_first = (keep_first > 0 && window > 0) ? keep_first : 0;
+    p.softcap = softcap > 0.f ? softcap : 0.f; p.rel = rel; p.rel_len = rel_len;
     if (qkv && (dist || p.keep_first)) return BW_ERR_UNSUPPORTED;
     if (gate && gate_dv < 0 ? (-gate_dv > HD || gate_ld < (long long)nh)
                             : gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;

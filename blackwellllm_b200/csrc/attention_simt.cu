@@ -24,7 +24,8 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
                       int max_blocks, OT* __restrict__ out, int nh, int nkv, int hd, int page_size,
                       int num_pages, int window, int chunk, float scale, const float* __restrict__ sink,
                       const float* __restrict__ gate, long long gate_ld, int gate_dv,
-                      const float* __restrict__ dist, int keep_first) {
+                      const float* __restrict__ dist, int keep_first, float softcap, const float* __restrict__ rel,
+                      int rel_len) {
     extern __shared__ float smem[];
     float* qs = smem;                       // [hd]
     float* accs = qs + hd;                  // [WARPS][hd]
@@ -65,7 +66,9 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
                 float d = 0.f;
                 for (int c = 0; c < hd; ++c) d = fmaf(qs[c], bw::to_f32(kr[c]), d);
                 s = d * scale;
+                if (softcap > 0.f) s = bw::soft_cap(s, softcap);
                 if (dist) s -= bw::distance_bias(r1, r2, q_pos - kp);
+                if (rel) s += bw::table_bias(rel + (size_t)h * rel_len, rel_len, q_pos - kp);
             }
         }
         const float cm = bw::warp_max(s);
@@ -121,20 +124,23 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
 // type: element type of q, the pages and out (all the same).  window <= 0: no window; chunk <= 0: no blocks (bw::first_visible).
 // dist: float32 [2, nh] (r1 of every head, then r2) or null: r1 ln(1 + r2 (query position - key position)) is taken off
 // every score.  keep_first: the first so many keys of a sequence stay visible whatever the window says.  gate_dv < 0:
-// one gate number per head (bw::out_gate).
+// one gate number per head (bw::out_gate).  softcap > 0: the scaled score s becomes softcap * tanh(s / softcap) before any
+// bias.  rel: float32 [nh][rel_len] or null: rel[head][min(query position - key position, rel_len - 1)] is added to the score.
 BW_EXPORT int bw_attention_simt(const void* q, const void* k_pages, const void* v_pages, int type,
                                 const int* positions, const int* req_of_token, const int* block_table,
                                 int max_blocks, void* out, int T, int nh, int nkv, int hd, int page_size,
                                 int num_pages, int window, int chunk, float scale, const float* sink, const float* gate,
-                                long long gate_ld, int gate_dv, const float* dist, int keep_first, void* stream) {
+                                long long gate_ld, int gate_dv, const float* dist, int keep_first, float softcap,
+                                const float* rel, int rel_len, void* stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > HD_LIMIT || nkv <= 0 || nh % nkv != 0) return BW_ERR_UNSUPPORTED;
+    if (rel && rel_len <= 0) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, nh);
     const size_t smem = (size_t)(hd + WARPS * hd + WARPS * 2) * sizeof(float);
 #define BW_SIMT(TY, CH) attention_simt_kernel<TY, TY, TY, CH><<<grid, WARPS * 32, smem, s>>>( \
         (const TY*)q, (const TY*)k_pages, (const TY*)v_pages, positions, req_of_token, block_table, max_blocks, (TY*)out, nh, \
-        nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv, dist, keep_first)
+        nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv, dist, keep_first, softcap, rel, rel_len)
     if (type == BW_F32) { if (hd <= 256) BW_SIMT(float, 8); else BW_SIMT(float, 32); }
     else if (type == BW_BF16) { if (hd <= 256) BW_SIMT(bf16, 8); else BW_SIMT(bf16, 32); }
 #undef BW_SIMT

@@ -63,6 +63,9 @@ struct Params {
     // dist != null: float32 [2][nh] (r1 of every query head, then r2): r1 ln(1 + r2 (i - j)) is taken off the score of
     // query position i and key position j.  keep_first: with a window, the first so many keys of a sequence stay visible.
     const float* dist; int keep_first;
+    // softcap > 0: the scaled score s becomes softcap * tanh(s / softcap) before a bias is added.  rel != null: float32
+    // [nh][rel_len], rel[query head][min(i - j, rel_len - 1)] is added to the score.  (Not together with dist.)
+    float softcap; const float* rel; int rel_len;
 };
 
 // 2^x and log2(x), one MUFU instruction each
@@ -246,7 +249,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         bool ok = true;
         float r1 = 0.f, r2 = 0.f;
         if (p.dist && row_ok) { r1 = p.dist[g * p.G + hg]; r2 = p.dist[p.nh + g * p.G + hg]; }
-        const float sc = p.dist ? 1.f : p.scale_log2;   // what turns a kept score into a power of two
+        const bool mod = p.softcap > 0.f || p.rel != nullptr;
+        const float* rel_row = (p.rel && row_ok) ? p.rel + (size_t)(g * p.G + hg) * p.rel_len : nullptr;
+        const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+        const float sc = (p.dist || mod) ? 1.f : p.scale_log2;   // what turns a kept score into a power of two
 
         for (int i = 0; i < n_tiles; ++i) {
             if (!__all_sync(0xffffffffu, bw::mbar_wait(s_full + 8 * (i & 1), (i >> 1) & 1, &g_status, 16))) { ok = false; break; }
@@ -269,6 +275,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 for (int c = 0; c < BN; ++c) {
                     const float b = fast_log2(fmaf(r2, fmaxf(d0 - (float)c, 0.f), 1.f));
                     v[c] = __float_as_uint(fmaf(-r1, b, __uint_as_float(v[c]) * p.scale_log2));
+                }
+            }
+            if (mod) {
+                // (uniform over the launch) the scores capped, the table's entry of the distance added, in powers of two
+                const float scale = p.scale_log2 * 0.6931471805599453f;
+                const int d0 = qpos - key0;
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    float x = __uint_as_float(v[c]) * scale;
+                    if (p.softcap > 0.f) x = bw::soft_cap_fast(x, p.softcap, inv_cap);
+                    if (rel_row) x += bw::table_bias(rel_row, p.rel_len, d0 - c > 0 ? d0 - c : 0);
+                    v[c] = __float_as_uint(x * 1.4426950408889634f);
                 }
             }
             if (need_mask) {   // one branch per tile, not one per key
@@ -437,13 +455,15 @@ BW_EXPORT int bw_attention_tc_supported(int nh, int nkv, int page_size) {
 
 // work: n_items int4 (request, first token of the 128-row tile within the request's segment, 0, 0);
 // a tile holds 128 / G tokens.  q, out: [T, nh * HD] bf16; pages: [num_pages, nkv, page_size, HD] bf16.
-// dist: float32 [2][nh] or null; keep_first: see Params.
+// dist: float32 [2][nh] or null; keep_first: see Params.  softcap (> 0: on), rel, rel_len: see Params.
 BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
                               const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
                               const int* work, int n_items, int T, int nh, int nkv, int page_size, int num_pages,
                               int window, int chunk, float scale, const float* sink, const float* gate, long long gate_ld,
-                              int gate_dv, const float* dist, int keep_first, void* stream) {
+                              int gate_dv, const float* dist, int keep_first, float softcap, const float* rel, int rel_len,
+                              void* stream) {
     if (n_items <= 0) return 0;
+    if ((rel && rel_len <= 0) || ((rel || softcap > 0.f) && dist)) return BW_ERR_UNSUPPORTED;
     if (!bw_attention_tc_supported(nh, nkv, page_size) || !(scale > 0.f)) return BW_ERR_UNSUPPORTED;
     if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return BW_ERR_UNSUPPORTED;
     const int G = nh / nkv, tpt = BM / G;
@@ -472,6 +492,7 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
                             : gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;
     p.gate = gate; p.gate_ld = gate_ld; p.gate_dv = gate_dv;
     p.dist = dist; p.keep_first = (keep_first > 0 && p.window > 0) ? keep_first : 0;
+    p.softcap = softcap > 0.f ? softcap : 0.f; p.rel = rel; p.rel_len = rel_len;
     bw::launch((attn_tc_kernel), dim3((unsigned)n_items * nkv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, tq, tk, tv, p);
     BW_LAUNCH_CHECK();
     return 0;

@@ -132,6 +132,20 @@ __device__ __forceinline__ float distance_bias(float r1, float r2, int dist) {
     return r1 * log1pf(r2 * (float)dist);
 }
 
+// A soft cap on a score: cap * tanh(s / cap).  soft_cap: the library's tanh (the 32-bit path).  soft_cap_fast: tanh as
+// 1 - 2 / (2^(2 x log2 e) + 1) with the fast exponential and division; its error is a few ulps of 1, so a few 1e-7 * cap.
+__device__ __forceinline__ float soft_cap(float s, float cap) { return cap * tanhf(s / cap); }
+__device__ __forceinline__ float soft_cap_fast(float s, float cap, float inv_cap) {
+    const float e = exp2f(s * inv_cap * 2.8853900817779268f);
+    return cap * (1.f - __fdividef(2.f, e + 1.f));
+}
+
+// A learned bias per (query head, distance): table float32 [heads][len], the last entry standing for every distance
+// from len - 1 on.
+__device__ __forceinline__ float table_bias(const float* __restrict__ head_row, int len, int dist) {
+    return head_row[dist < len ? dist : len - 1];
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);   // lo in the low half
     return *reinterpret_cast<const uint32_t*>(&v);

@@ -59,13 +59,13 @@ __global__ void embed_positions_kernel(const WT* __restrict__ table, const int* 
 template <typename WT, typename OT>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict__ w,
                                const int* __restrict__ rows, OT* __restrict__ out,
-                               int H, float eps) {
+                               int H, float eps, long long ld) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const int src = rows ? rows[i] : i;
-    const float* xr = x + (size_t)src * H;
+    const float* xr = x + (size_t)src * (size_t)ld;
     OT* o = out + (size_t)i * H;
     float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) { float v = xr[c]; ss = fmaf(v, v, ss); }
@@ -94,13 +94,13 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 
 template <typename WT, typename OT>
 __global__ void rmsnorm_vec4_kernel(const float* __restrict__ x, const WT* __restrict__ w,
-                                    const int* __restrict__ rows, OT* __restrict__ out, int H, float eps) {
+                                    const int* __restrict__ rows, OT* __restrict__ out, int H, float eps, long long ld) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const int src = rows ? rows[i] : i;
-    const float* xr = x + (size_t)src * H;
+    const float* xr = x + (size_t)src * (size_t)ld;
     OT* o = out + (size_t)i * H;
     float ss = 0.f;
     for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
@@ -203,6 +203,20 @@ __global__ void sum_planes_kernel(float* __restrict__ x, const float* __restrict
         float v = 0.f;
         add_planes1(v, planes + i, n_planes, plane_stride);
         x[i] = v;
+    }
+}
+
+// x[t, c] += a[t, c] * ga[c] (+ b[t, c] * gb[c]): sublayers' outputs, each times a gain per channel ("layer scale"),
+// summed and added to the stream.  The two products are added to each other first, then to x.
+__global__ void scale_add_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ ga,
+                                 const float* __restrict__ b, const float* __restrict__ gb, size_t total, int H) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % (size_t)H);
+        float y = a[i] * ga[c];
+        if (b) y += b[i] * gb[c];
+        x[i] += y;
     }
 }
 
@@ -479,14 +493,16 @@ BW_EXPORT int bw_embed_positions(const void* table, int table_type, const int* i
     return 0;
 }
 
-BW_EXPORT int bw_rmsnorm(const float* x, const void* w, int w_type, const int* rows, void* out,
-                         int out_type, int n_rows, int H, float eps, void* stream) {
+// the rows of x lie `ld` floats apart (ld >= H: x may be a range of columns of a wider tensor); out is dense
+BW_EXPORT int bw_rmsnorm_ld(const float* x, long long ld, const void* w, int w_type, const int* rows, void* out,
+                            int out_type, int n_rows, int H, float eps, void* stream) {
     if (n_rows <= 0) return 0;
+    if (ld < H) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    const bool vec = H % 4 == 0 && ld % 4 == 0 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
     const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
-#define BW_RMS(WT, OT) do { if (vec) bw::launch((rmsnorm_vec4_kernel<WT, OT>), dim3(n_rows), dim3(threads), 0, s, x, cp<WT>(w), rows, mp<OT>(out), H, eps); \
-        else bw::launch((rmsnorm_kernel<WT, OT>), dim3(n_rows), dim3(threads), 0, s, x, cp<WT>(w), rows, mp<OT>(out), H, eps); } while (0)
+#define BW_RMS(WT, OT) do { if (vec) bw::launch((rmsnorm_vec4_kernel<WT, OT>), dim3(n_rows), dim3(threads), 0, s, x, cp<WT>(w), rows, mp<OT>(out), H, eps, ld); \
+        else bw::launch((rmsnorm_kernel<WT, OT>), dim3(n_rows), dim3(threads), 0, s, x, cp<WT>(w), rows, mp<OT>(out), H, eps, ld); } while (0)
     if (w_type == BW_F32 && out_type == BW_F32) BW_RMS(float, float);
     else if (w_type == BW_F32 && out_type == BW_BF16) BW_RMS(float, bf16);
     else if (w_type == BW_BF16 && out_type == BW_F32) BW_RMS(bf16, float);
@@ -495,6 +511,11 @@ BW_EXPORT int bw_rmsnorm(const float* x, const void* w, int w_type, const int* r
 #undef BW_RMS
     BW_LAUNCH_CHECK();
     return 0;
+}
+
+BW_EXPORT int bw_rmsnorm(const float* x, const void* w, int w_type, const int* rows, void* out,
+                         int out_type, int n_rows, int H, float eps, void* stream) {
+    return bw_rmsnorm_ld(x, H, w, w_type, rows, out, out_type, n_rows, H, eps, stream);
 }
 
 // x[n_rows or more, H] += the planes (float32, plane_stride floats apart), out = rmsnorm of the new x.
@@ -567,6 +588,18 @@ BW_EXPORT int bw_add_planes(float* x, const float* planes, int n_planes, long lo
     const long long want = (total + 255) / 256;
     bw::launch(add_planes_kernel, dim3((unsigned)(want < 148 * 8 ? want : 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
                x, planes, n_planes, (size_t)plane_stride, (size_t)total);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+// x, a (and b, or null): float32 [T, H]; ga (gb): float32 [H]
+BW_EXPORT int bw_scale_add(float* x, const float* a, const float* ga, const float* b, const float* gb, int T, int H,
+                           void* stream) {
+    if (T <= 0) return 0;
+    if (!x || !a || !ga || H <= 0 || (b != nullptr) != (gb != nullptr)) return BW_ERR_BAD_ARG;
+    const long long total = (long long)T * H, want = (total + 255) / 256;
+    bw::launch(scale_add_kernel, dim3((unsigned)(want < 148 * 8 ? want : 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
+               x, a, ga, b, gb, (size_t)total, H);
     BW_LAUNCH_CHECK();
     return 0;
 }

@@ -40,6 +40,13 @@ struct ScanParams {
     int q_off, k_off, v_off;
     int heads, dk, dv;
     float q_scale;
+    // The same recurrence serves a matrix memory with ONE decay per head and token and a normaliser:
+    // scalar_decay != 0: decay is [T, heads] (a_t of the head, used for every key channel);
+    // k_scale != null: [T, heads], the token's keys are multiplied by it as they are read (an input gate);
+    // ones_col != 0: the head's last value column (dv - 1) is the constant 1 and v holds dv - 1 columns a head, so that
+    // column of the state is n_t = a_t n_(t-1) + k_t and the last output column is n_t . q_t.
+    const float* k_scale;
+    int scalar_decay, ones_col;
 };
 
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -117,14 +124,18 @@ gla_scan_kernel(ScanParams p) {
                 const float* row = p.qkv + (size_t)(tb + tt) * p.ld;
                 rq[u] = row[p.q_off + h * p.dk + i];
                 rk[u] = row[p.k_off + h * p.dk + i];
-                ra[u] = p.decay[(size_t)(tb + tt) * p.heads * p.dk + h * p.dk + i];
+                if (p.k_scale) rk[u] *= p.k_scale[(size_t)(tb + tt) * p.heads + h];
+                ra[u] = p.scalar_decay ? p.decay[(size_t)(tb + tt) * p.heads + h]
+                                       : p.decay[(size_t)(tb + tt) * p.heads * p.dk + h * p.dk + i];
             }
         }
+        const int dv_in = p.dv - (p.ones_col ? 1 : 0);   // value columns a head has in memory
 #pragma unroll
         for (int u = 0; u < NSV; ++u) {
             const int idx = threadIdx.x + u * THREADS;
             const int tt = idx / COLS, cc = idx % COLS;
-            rv[u] = (tt < n && c0 + cc < p.dv) ? p.qkv[(size_t)(tb + tt) * p.ld + p.v_off + h * p.dv + c0 + cc] : 0.f;
+            rv[u] = (tt < n && c0 + cc < dv_in) ? p.qkv[(size_t)(tb + tt) * p.ld + p.v_off + h * dv_in + c0 + cc]
+                                                : ((tt < n && p.ones_col && c0 + cc == dv_in) ? 1.f : 0.f);
         }
     };
     if (t0 < t1) fetch(t0, min(TOK_CHUNK, t1 - t0));
@@ -215,17 +226,19 @@ gla_gate_kernel(const float* __restrict__ o, const float* __restrict__ g, long l
 
 }  // namespace
 
-// decay: float32 [T, heads * dk] from bw_gla_decay
+// decay: float32 [T, heads * dk] from bw_gla_decay; with scalar_decay [T, heads].  k_scale: float32 [T, heads] or null.
+// ones_col != 0: dv counts a last column of ones that v does not hold (state [slots, heads, dk, dv], o [T, heads * dv]).
 BW_EXPORT int bw_gla_scan(const float* qkv, long long ld, int q_off, int k_off, int v_off, const float* decay,
                           const int* cu_q, const int* state_slot, float* state, float* o, int R, int heads, int dk,
-                          int dv, float q_scale, void* stream) {
+                          int dv, float q_scale, const float* k_scale, int scalar_decay, int ones_col, void* stream) {
     if (R <= 0) return 0;
-    if (heads <= 0 || dk <= 0 || dv <= 0) return BW_ERR_BAD_ARG;
+    if (heads <= 0 || dk <= 0 || dv <= 0 || (ones_col && dv < 2)) return BW_ERR_BAD_ARG;
     if (dk > MAX_DK) return BW_ERR_UNSUPPORTED;
     ScanParams p;
     p.qkv = qkv; p.decay = decay; p.cu_q = cu_q; p.state_slot = state_slot; p.state = state; p.o = o; p.ld = ld;
     p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.heads = heads; p.dk = dk; p.dv = dv;
     p.q_scale = q_scale;
+    p.k_scale = k_scale; p.scalar_decay = scalar_decay; p.ones_col = ones_col;
     const dim3 grid(R, heads, (dv + COLS - 1) / COLS);
     const int rpl = dk <= 128 ? 4 : 8;
     const size_t smem = (size_t)(3 * TOK_CHUNK * 32 * rpl + TOK_CHUNK * COLS) * sizeof(float);

@@ -16,7 +16,8 @@ namespace {
 
 template <typename OT>
 __global__ void __launch_bounds__(256)
-latent_prep_kernel(const float* __restrict__ proj, long long ld, int q_off, int kv_off, const int* __restrict__ positions,
+latent_prep_kernel(const float* __restrict__ qsrc, long long q_ld, int q_off, const float* __restrict__ proj, long long ld,
+                   int kv_off, int interleaved, const int* __restrict__ positions,
                    const int* __restrict__ req_of_token, const int* __restrict__ block_table, int max_blocks,
                    const float* __restrict__ table, const float* __restrict__ c_gain, float eps, OT* __restrict__ q_out,
                    OT* __restrict__ k_pages, int H, int d, int dr, int rank, int dpad, int page_size, int num_pages) {
@@ -25,19 +26,22 @@ latent_prep_kernel(const float* __restrict__ proj, long long ld, int q_off, int 
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const float* row = proj + (size_t)t * ld;
+    const float* qrow = qsrc + (size_t)t * q_ld;
     const float* tab = table + (size_t)t * dr;     // cosines, then sines (both already times the magnitude)
     const int half = dr >> 1;
+    // channel c turns with channel c + dr / 2 (pair c mod dr / 2), or, interleaved, channel 2j with channel 2j + 1 (pair j)
     auto turned = [&](const float* src, int c) {
-        const bool first = c < half;
-        const int j = first ? c : c - half;
-        const float x = src[c], y = src[first ? c + half : c - half];
+        const bool first = interleaved ? !(c & 1) : c < half;
+        const int j = interleaved ? c >> 1 : (first ? c : c - half);
+        const int pc = interleaved ? c ^ 1 : (first ? c + half : c - half);
+        const float x = src[c], y = src[pc];
         return first ? x * tab[j] - y * tab[half + j] : x * tab[j] + y * tab[half + j];
     };
     // the queries' rotated parts, behind the room for the absorbed plain parts; pad channels zero
     const int tail = dpad - rank;
     for (int idx = threadIdx.x; idx < H * tail; idx += blockDim.x) {
         const int h = idx / tail, c = idx - h * tail;
-        const float o = c < dr ? turned(row + q_off + (size_t)h * (d + dr) + d, c) : 0.f;
+        const float o = c < dr ? turned(qrow + q_off + (size_t)h * (d + dr) + d, c) : 0.f;
         q_out[((size_t)t * H + h) * dpad + rank + c] = bw::from_f32<OT>(o);
     }
     if (num_pages <= 0) return;
@@ -213,21 +217,27 @@ headwise_mma_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const bf1
 // projection at column kv_off: rank channels, then the dr channels of the shared key part.  table float32 [T, dr].
 // q_out [T, H, dpad] and the pages [num_pages, 1, page_size, dpad] of out_type, dpad >= rank + dr.  Channels
 // [0, rank) of q_out are left for headwise_linear.  num_pages <= 0: nothing is appended.
-BW_EXPORT int bw_latent_prep(const float* proj, long long ld, int q_off, int kv_off, const int* positions,
+// qsrc: the queries' rows (float32, q_ld apart, H heads of d + dr channels from column q_off on); proj: the rows that hold
+// the latent and the shared key part at column kv_off (the same tensor as qsrc, or another).  interleaved != 0: the rotation
+// pairs channel 2j with channel 2j + 1 instead of channel c with channel c + dr / 2.
+BW_EXPORT int bw_latent_prep(const float* qsrc, long long q_ld, int q_off, const float* proj, long long ld, int kv_off,
+                             int interleaved, const int* positions,
                              const int* req_of_token, const int* block_table, int max_blocks, const float* table,
                              const float* c_gain, float eps, void* q_out, void* k_pages, int out_type, int T, int H, int d,
                              int dr, int rank, int dpad, int page_size, int num_pages, void* stream) {
     if (T <= 0) return 0;
     if (H <= 0 || d <= 0 || dr <= 0 || (dr & 1) || rank <= 0 || dpad < rank + dr || page_size <= 0 || !table || !c_gain ||
-        ld < (long long)q_off + (long long)H * (d + dr) || ld < (long long)kv_off + rank + dr)
+        !qsrc || !proj || q_ld < (long long)q_off + (long long)H * (d + dr) || ld < (long long)kv_off + rank + dr)
         return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (out_type == BW_F32)
-        bw::launch((latent_prep_kernel<float>), dim3(T), dim3(256), 0, s, proj, ld, q_off, kv_off, positions, req_of_token,
+        bw::launch((latent_prep_kernel<float>), dim3(T), dim3(256), 0, s, qsrc, q_ld, q_off, proj, ld, kv_off, interleaved,
+                   positions, req_of_token,
                    block_table, max_blocks, table, c_gain, eps, (float*)q_out, (float*)k_pages, H, d, dr, rank, dpad,
                    page_size, num_pages);
     else if (out_type == BW_BF16)
-        bw::launch((latent_prep_kernel<bf16>), dim3(T), dim3(256), 0, s, proj, ld, q_off, kv_off, positions, req_of_token,
+        bw::launch((latent_prep_kernel<bf16>), dim3(T), dim3(256), 0, s, qsrc, q_ld, q_off, proj, ld, kv_off, interleaved,
+                   positions, req_of_token,
                    block_table, max_blocks, table, c_gain, eps, (bf16*)q_out, (bf16*)k_pages, H, d, dr, rank, dpad,
                    page_size, num_pages);
     else return BW_ERR_BAD_ARG;

@@ -101,7 +101,9 @@ __device__ __forceinline__ void put4(bf16* p, float4 v) {
 // grows with the logarithm of the position.  Rows of qkv are `ld` floats apart and hold the queries first,
 // then (has_kv != 0) keys and values; whatever follows in the row (a gate's projection) is not touched.
 // has_kv == 0: a run that reads another run's keys and values projects none.  One block per token, one warp
-// per head at a time; all arithmetic float32.
+// per head at a time; all arithmetic float32.  v_first != null: the values become (1 - lam) v + lam v_first on their way
+// into the cache, v_first being float32 rows `v_first_ld` apart with nkv * dv values of the same token (another layer's
+// values of this step) and lam = *v_lam a number on the device.
 template <typename OT>
 __global__ void __launch_bounds__(256)
 head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __restrict__ positions,
@@ -111,7 +113,7 @@ head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __
                       float q_coef, float q_every,
                       OT* __restrict__ q_out, OT* __restrict__ k_pages, OT* __restrict__ v_pages,
                       int nh, int nkv, int dq, int dv, int dpad, int page_size, int num_pages, int has_kv, int vec,
-                      float v_eps) {
+                      float v_eps, const float* __restrict__ v_first, long long v_first_ld, const float* __restrict__ v_lam) {
     BW_PDL_TRIGGER();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -177,21 +179,24 @@ head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __
             dst[c] = bw::from_f32<OT>(o);
         }
     }
+    // a value as it is cached: mixed with the same token's value of another layer where the launch says so
+    const float* vsrc = row + nq + nk;
+    const float* vf = v_first ? v_first + (size_t)t * v_first_ld : nullptr;
+    const float lam = v_first ? *v_lam : 0.f;
+    auto value = [&](size_t i) { const float v = vsrc[i]; return vf ? (1.f - lam) * v + lam * vf[i] : v; };
     if (page >= 0 && v_eps > 0.f) {
         // every value head divided by its own root mean square (no gain): a warp per head
-        const float* vsrc = row + nq + nk;
         for (int h = warp; h < nkv; h += nwarps) {
             float ss = 0.f;
-            for (int c = lane; c < dv; c += 32) { const float v = vsrc[(size_t)h * dv + c]; ss = fmaf(v, v, ss); }
+            for (int c = lane; c < dv; c += 32) { const float v = value((size_t)h * dv + c); ss = fmaf(v, v, ss); }
             const float r = rsqrtf(bw::warp_sum(ss) / (float)dv + v_eps);
             OT* dst = v_pages + (((size_t)page * nkv + h) * page_size + slot) * dpad;
-            for (int c = lane; c < dpad; c += 32) dst[c] = bw::from_f32<OT>(c < dv ? vsrc[(size_t)h * dv + c] * r : 0.f);
+            for (int c = lane; c < dpad; c += 32) dst[c] = bw::from_f32<OT>(c < dv ? value((size_t)h * dv + c) * r : 0.f);
         }
         return;
     }
     if (page >= 0) {
-        const float* vsrc = row + nq + nk;
-        if (vec) {
+        if (vec && !vf) {
             for (int idx = threadIdx.x * 4; idx < nkv * dpad; idx += blockDim.x * 4) {
                 const int h = idx / dpad, c = idx - h * dpad;
                 const float4 o = c < dv ? *reinterpret_cast<const float4*>(vsrc + (size_t)h * dv + c) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -201,7 +206,7 @@ head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __
         }
         for (int idx = threadIdx.x; idx < nkv * dpad; idx += blockDim.x) {
             const int h = idx / dpad, c = idx - h * dpad;
-            const float o = c < dv ? vsrc[(size_t)h * dv + c] : 0.f;
+            const float o = c < dv ? value((size_t)h * dv + c) : 0.f;
             v_pages[(((size_t)page * nkv + h) * page_size + slot) * dpad + c] = bw::from_f32<OT>(o);
         }
     }
@@ -212,24 +217,26 @@ head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __
 // The per-head form (head_norm_rope_kernel).  ld: floats between rows of qkv; q_gain / k_gain: float32 [dq] or
 // null; q_coef, q_every: the queries' temperature (q_coef == 0: none; q_every > 0); has_kv == 0: the rows hold
 // no keys and values and nothing is appended.  v_eps > 0: every value head is divided by sqrt(mean(v^2) + v_eps) on its way
-// into the cache.
+// into the cache.  v_first, v_first_ld, v_lam: the value mixing (see the kernel), or nulls.
 BW_EXPORT int bw_head_norm_rope_append(const float* qkv, long long ld, const int* positions, const int* req_of_token,
                                        const int* block_table, int max_blocks, const float* table, int rotary_dim,
                                        int interleaved, const float* q_gain, const float* k_gain, float eps,
                                        float q_coef, float q_every, void* q_out, void* k_pages, void* v_pages,
                                        int out_type, int T, int nh, int nkv, int dq, int dv, int dpad, int page_size,
-                                       int num_pages, int has_kv, float v_eps, void* stream) {
+                                       int num_pages, int has_kv, float v_eps, const float* v_first, long long v_first_ld,
+                                       const float* v_lam, void* stream) {
     if (T <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > dq || (rotary_dim & 1) || dq <= 0 || dv <= 0 || dpad < dq || dpad < dv ||
         nh <= 0 || nkv <= 0 || page_size <= 0 || (rotary_dim > 0 && !table) || (q_coef != 0.f && !(q_every > 0.f)) ||
-        ld < (long long)nh * dq + (has_kv ? (long long)nkv * (dq + dv) : 0))
+        ld < (long long)nh * dq + (has_kv ? (long long)nkv * (dq + dv) : 0) ||
+        (v_first && (!v_lam || !has_kv || v_first_ld < (long long)nkv * dv)))
         return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const int vec = rotary_dim == 0 && (dq & 3) == 0 && (dv & 3) == 0 && (dpad & 3) == 0 && (ld & 3) == 0 &&
                     (((uintptr_t)qkv | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
 #define BW_HN(OT) bw::launch((head_norm_rope_kernel<OT>), dim3(T), dim3(256), 0, s, qkv, ld, positions, req_of_token, block_table, \
         max_blocks, table, rotary_dim, interleaved, q_gain, k_gain, eps, q_coef, q_every, (OT*)q_out, (OT*)k_pages, (OT*)v_pages, \
-        nh, nkv, dq, dv, dpad, page_size, num_pages, has_kv, vec, v_eps)
+        nh, nkv, dq, dv, dpad, page_size, num_pages, has_kv, vec, v_eps, v_first, v_first_ld, v_lam)
     if (out_type == BW_F32) BW_HN(float);
     else if (out_type == BW_BF16) BW_HN(bf16);
     else return BW_ERR_BAD_ARG;

@@ -6,6 +6,7 @@ implementation.
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 from typing import Optional
 
@@ -290,7 +291,10 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
 
 
 def _rmsnorm(x, w, eps, out_dtype, rows, out, planes):
-    _dev(x, "x", torch.float32); _dev(w, "w")
+    # (x may be a range of columns of a wider tensor when nothing is to be added to it)
+    _dev(x, "x", torch.float32, contiguous=planes is not None); _dev(w, "w")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("rmsnorm: x must be [rows, H] with contiguous rows")
     H = x.shape[-1]
     if w.numel() != H:
         raise KernelError(f"rmsnorm: gain has {w.numel()} elements, rows have {H}")
@@ -306,9 +310,9 @@ def _rmsnorm(x, w, eps, out_dtype, rows, out, planes):
         _check(fn(_ptr(x), _ptr(planes), planes.shape[0], planes.stride(0), _ptr(w), _code(w, "w"), _ptr(rows), _ptr(out),
                   _code(out, "out"), n, H, float(eps), _stream()), "add_rmsnorm")
         return out
-    fn = _fn("elementwise", "bw_rmsnorm",
-             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
-    _check(fn(_ptr(x), _ptr(w), _code(w, "w"), _ptr(rows), _ptr(out), _code(out, "out"), n, H,
+    fn = _fn("elementwise", "bw_rmsnorm_ld",
+             [c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(x), x.stride(0), _ptr(w), _code(w, "w"), _ptr(rows), _ptr(out), _code(out, "out"), n, H,
               float(eps), _stream()), "rmsnorm")
     return out
 
@@ -478,10 +482,12 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
                    req_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, window: Optional[int],
                    scale: float, out: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
                    sink: Optional[torch.Tensor] = None, gate: Optional[tuple] = None,
-                   dist: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
+                   dist: Optional[torch.Tensor] = None, keep_first: int = 0, softcap: Optional[float] = None,
+                   rel: Optional[torch.Tensor] = None) -> torch.Tensor:
     _dev(q, "q"); _dev(k_pages, "k_pages", q.dtype); _dev(v_pages, "v_pages", q.dtype)
     _check_sink(sink, nh)
     _check_dist(dist, nh)
+    _check_rel(rel, nh, dist)
     g, g_ld, g_dv = _gate_args(gate, q.shape[0], nh, k_pages.shape[3])
     _dev(positions, "positions", torch.int32); _dev(req_of_token, "req_of_token", torch.int32)
     _dev(block_table, "block_table", torch.int32)
@@ -493,11 +499,13 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
         out = torch.empty_like(q)
     fn = _fn("attention_simt", "bw_attention_simt",
              [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_int, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_int,
+              c_float, c_void_p, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q, "q"), _ptr(positions), _ptr(req_of_token),
               _ptr(block_table), block_table.shape[1], _ptr(out), T, nh, nkv, hd, page_size, num_pages,
               int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _ptr(g), g_ld, g_dv, _ptr(dist),
-              int(keep_first or 0), _stream()), "attention_simt")
+              int(keep_first or 0), float(softcap or 0.0), _ptr(rel), rel.shape[1] if rel is not None else 0,
+              _stream()), "attention_simt")
     return out
 
 
@@ -530,6 +538,38 @@ def _check_dist(dist: Optional[torch.Tensor], nh: int) -> None:
         _dev(dist, "dist", torch.float32)
         if tuple(dist.shape) != (2, nh):
             raise KernelError(f"attention: the distance bias must be float32 [2, {nh}] (r1 of every head, then r2)")
+
+
+def _check_rel(rel: Optional[torch.Tensor], nh: int, dist: Optional[torch.Tensor] = None) -> None:
+    if rel is not None:
+        _dev(rel, "rel", torch.float32)
+        if rel.dim() != 2 or rel.shape[0] != nh or rel.shape[1] < 1:
+            raise KernelError(f"attention: the table of biases by distance must be float32 [{nh}, distances]")
+        if dist is not None:
+            raise KernelError("attention: a table of biases by distance does not go with the logarithmic distance bias")
+
+
+def distance_bucket_table(rows: int, far: float) -> torch.Tensor:
+    """int64 [n]: the row of a table of ``rows`` learned biases that stands for the distance d = 0 .. n - 1 between a
+    query and a key: distances below rows / 2 have a row each, larger ones share rows on a logarithmic scale that
+    reaches the last row at distance ``far``: min(rows - 1, half + floor(ln(d / half) / ln(far / half) * (rows - half))),
+    half = rows // 2.  n - 1 is the first distance that takes the last row (every larger one takes it too), so entry
+    n - 1 stands for all of them.  Host arithmetic in float64."""
+    half = rows // 2
+    if rows < 1 or (rows > 1 and half >= 1 and not far > half):
+        raise KernelError(f"distance_bucket_table: {rows} rows need a farthest distance above {half}, got {far}")
+    out = []
+    d = 0
+    while True:
+        if d < half or half == 0:
+            b = min(d, rows - 1)
+        else:
+            b = min(rows - 1, half + int(math.floor(math.log(d / half) / math.log(far / half) * (rows - half))))
+        out.append(b)
+        if b >= rows - 1 or d > 1 << 24:
+            break
+        d += 1
+    return torch.tensor(out, dtype=torch.int64)
 
 
 # ------------------------------------------------------------------ sampling
@@ -813,7 +853,8 @@ def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
                     block_table: torch.Tensor, nh: int, window: Optional[int], scale: float,
                     chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None,
                     gate: Optional[tuple] = None, dist: Optional[torch.Tensor] = None,
-                    keep_first: int = 0) -> torch.Tensor:
+                    keep_first: int = 0, softcap: Optional[float] = None,
+                    rel: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the batch's tokens over the paged cache (which already
     holds this step's keys and values, unless ``q`` is an :class:`UnrotatedQKV`).  float32: the
     CUDA-core kernel; bfloat16: the tensor-core kernel built for this head size.  A query sees the keys
@@ -824,26 +865,33 @@ def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
     sigmoid(g[t, head * dv + c]) as it is written; channels from dv on (padding) become zero; (g [T, nh], dv, "head"):
     one gate number per head.  ``dist`` (float32 [2, nh]: r1 of every head, then r2): r1 ln(1 + r2 (i - j)) is taken off
     the score of query position i and key position j.  ``keep_first``: the first so many keys of a sequence stay
-    visible beyond the window."""
+    visible beyond the window.  ``softcap``: the scaled score s becomes softcap * tanh(s / softcap) before any bias.
+    ``rel`` (float32 [nh, n]): rel[head, min(i - j, n - 1)] is added to the score (a learned bias per distance, its last
+    entry standing for every larger distance; :func:`distance_bucket_table` says which distances share a learned row)."""
+    if (softcap or rel is not None) and isinstance(q, UnrotatedQKV):
+        q = q.materialise()
     if isinstance(q, UnrotatedQKV):
         if batch.T == batch.R and attention_takes_unrotated(k_pages.shape[3], k_pages.shape[2]):
             return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate)
         q = q.materialise()
     if q.dtype == torch.float32:
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
-                              window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first)
+                              window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first,
+                              softcap=softcap, rel=rel)
     if nh // k_pages.shape[1] > MAX_GROUP_BF16 or k_pages.shape[3] > 256:
         # more query heads per kv head than a tile of the tensor-core kernels stacks, or a head size beyond the ones
         # they are built for (a wide latent row): the CUDA-core kernel in bfloat16
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
-                              window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first)
-    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate, dist, keep_first)
+                              window, scale, chunk=chunk, sink=sink, gate=gate, dist=dist, keep_first=keep_first,
+                              softcap=softcap, rel=rel)
+    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate, dist, keep_first,
+                         softcap, rel)
 
 
 _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                    c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_int,
-                                   c_void_p, c_int, c_void_p]
+                                   c_void_p, c_int, c_float, c_void_p, c_int, c_void_p]
 
 
 _sm_counts = {}
@@ -933,10 +981,15 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
 def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_table: torch.Tensor,
                   nh: int, window: Optional[int], scale: float, chunk: Optional[int] = None,
                   sink: Optional[torch.Tensor] = None, gate: Optional[tuple] = None,
-                  dist: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
+                  dist: Optional[torch.Tensor] = None, keep_first: int = 0, softcap: Optional[float] = None,
+                  rel: Optional[torch.Tensor] = None) -> torch.Tensor:
     _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
     _check_sink(sink, nh)
     _check_dist(dist, nh)
+    _check_rel(rel, nh, dist)
+    if softcap and dist is not None:
+        raise KernelError("attention: a soft cap on the scores does not go with the logarithmic distance bias")
+    rel_len = rel.shape[1] if rel is not None else 0
     keep_first = int(keep_first or 0) if window else 0
     g, g_ld, g_dv = _gate_args(gate, batch.T, nh, k_pages.shape[3])
     _dev(block_table, "block_table", torch.int32)
@@ -980,7 +1033,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
         _check(tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
                   _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, q.shape[0],
                   nh, nkv, page_size, num_pages, int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _ptr(g), g_ld, g_dv,
-                  _ptr(dist), keep_first, _stream()), "attention_tc")
+                  _ptr(dist), keep_first, float(softcap or 0.0), _ptr(rel), rel_len, _stream()), "attention_tc")
         n_rows = 0
         if not n_keys:
             return out
@@ -992,12 +1045,13 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
               _ptr(raw.planes if raw is not None else None), raw.planes.shape[0] if raw is not None else 0,
               raw.planes.stride(0) if raw is not None else 0, _ptr(raw.table if raw is not None else None),
               raw.rotary_dim if raw is not None else 0, int(raw.append) if raw is not None else 0, merge_max,
-              _ptr(sink), _ptr(g), g_ld, g_dv, _ptr(dist), keep_first, _stream()), "attention_mma")
+              _ptr(sink), _ptr(g), g_ld, g_dv, _ptr(dist), keep_first, float(softcap or 0.0), _ptr(rel), rel_len,
+              _stream()), "attention_mma")
     return out
 
 
 _ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                  c_void_p, c_ll, c_int, c_void_p, c_int, c_void_p]
+                                  c_void_p, c_ll, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p]
 
 
 def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:
@@ -1087,6 +1141,23 @@ def add_into(target: torch.Tensor, other: torch.Tensor) -> torch.Tensor:
     return target
 
 
+def scale_add(stream: torch.Tensor, a: torch.Tensor, ga: torch.Tensor, b: Optional[torch.Tensor] = None,
+              gb: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``stream += a * ga (+ b * gb)``: sublayers' outputs (float32 [T, H]) times a gain per channel (float32 [H]) on
+    their way into the stream; the two products are added to each other first."""
+    _dev(stream, "stream", torch.float32); _dev(a, "a", torch.float32); _dev(ga, "ga", torch.float32)
+    T, H = stream.shape
+    if a.shape != (T, H) or ga.numel() != H or (b is None) != (gb is None):
+        raise KernelError("scale_add: a (and b) must have the stream's shape, the gains its width")
+    if b is not None:
+        _dev(b, "b", torch.float32); _dev(gb, "gb", torch.float32)
+        if b.shape != (T, H) or gb.numel() != H:
+            raise KernelError("scale_add: b must have the stream's shape, its gain the width")
+    fn = _fn("elementwise", "bw_scale_add", [c_void_p] * 5 + [c_int, c_int, c_void_p])
+    _check(fn(_ptr(stream), _ptr(a), _ptr(ga), _ptr(b), _ptr(gb), T, H, _stream()), "scale_add")
+    return stream
+
+
 # ------------------------------------------------------------------ q/k norm + rotation + append
 
 def qk_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, table: Optional[torch.Tensor],
@@ -1129,15 +1200,23 @@ def head_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, t
                           rotary_dim: int, interleaved: bool, q_gain: Optional[torch.Tensor],
                           k_gain: Optional[torch.Tensor], eps: float, k_pages: torch.Tensor, v_pages: torch.Tensor,
                           nh: int, nkv: int, dq: int, dv: int, has_kv: bool = True, append: bool = True,
-                          q_temp: Optional[tuple] = None, v_eps: float = 0.0) -> torch.Tensor:
+                          q_temp: Optional[tuple] = None, v_eps: float = 0.0,
+                          v_mix: Optional[tuple] = None) -> torch.Tensor:
     """:func:`qk_norm_rope_append` with the norm taken per head: every query head is divided by its own root mean
     square and multiplied by ``q_gain`` (float32 [dq], shared by the heads; ``k_gain`` for the key heads).
     ``qkv`` float32 [T, >= nh*dq (+ nkv*dq + nkv*dv with ``has_kv``)]: further columns (a gate's projection) are
     left alone.  ``q_temp`` = (coef, every): after norm and rotation the queries of a token at position p are
     multiplied by ``1 + coef * log(1 + n)``, n the whole periods of ``every`` positions in p + 1.  Without ``has_kv`` (a run that reads another
     run's keys and values) nothing is appended.  ``v_eps`` > 0: every value head is divided by
-    sqrt(mean(v^2) + v_eps) on its way into the cache."""
+    sqrt(mean(v^2) + v_eps) on its way into the cache.  ``v_mix`` = (v_first float32 [T, nkv * dv], possibly a column
+    range of a wider tensor; lam, a float32 number on the device): the values are cached as (1 - lam) v + lam v_first."""
     _dev(qkv, "qkv", torch.float32); _dev(block_table, "block_table", torch.int32)
+    vf = lam = None
+    if v_mix is not None:
+        vf, lam = v_mix
+        _dev(vf, "v_first", torch.float32, contiguous=False); _dev(lam, "lam", torch.float32)
+        if vf.shape != (qkv.shape[0], nkv * dv) or vf.stride(1) != 1 or lam.numel() != 1 or not has_kv:
+            raise KernelError("head_norm_rope_append: v_first must be float32 [T, nkv * dv] with contiguous rows, lam one number")
     _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)
     T = qkv.shape[0]
     num_pages, pk, page_size, dpad = k_pages.shape
@@ -1157,11 +1236,12 @@ def head_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, t
     q_out = torch.empty((T, nh * dpad), dtype=k_pages.dtype, device=qkv.device)
     fn = _fn("qk_norm_rope", "bw_head_norm_rope_append",
              [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float,
-              c_float, c_void_p, c_void_p, c_void_p] + [c_int] * 10 + [c_float, c_void_p])
+              c_float, c_void_p, c_void_p, c_void_p] + [c_int] * 10 + [c_float, c_void_p, c_ll, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), qkv.stride(0), _ptr(batch.positions), _ptr(batch.req_of_token), _ptr(block_table),
               block_table.shape[1], _ptr(table), int(rotary_dim), int(interleaved), _ptr(q_gain), _ptr(k_gain), float(eps),
               coef, every, _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _code(k_pages, "pages"), T, nh, nkv, dq, dv, dpad,
-              page_size, num_pages if (append and has_kv) else 0, int(has_kv), float(v_eps or 0.0), _stream()),
+              page_size, num_pages if (append and has_kv) else 0, int(has_kv), float(v_eps or 0.0), _ptr(vf),
+              vf.stride(0) if vf is not None else 0, _ptr(lam), _stream()),
            "head_norm_rope_append")
     return q_out
 
@@ -1230,22 +1310,28 @@ def concat2_cast(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> to
 
 def latent_prep(proj: torch.Tensor, q_off: int, kv_off: int, batch, block_table: torch.Tensor, table: torch.Tensor,
                 c_gain: torch.Tensor, eps: float, k_pages: torch.Tensor, H: int, d: int, dr: int, rank: int,
-                append: bool = True) -> torch.Tensor:
+                append: bool = True, q_src: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
     """From the projections of a step (float32 [T, ...]: H query heads of d plain + dr rotated channels at column
     ``q_off``; the latent's rank channels and the shared key part's dr channels at ``kv_off``): appends
     [rms_norm(latent) * c_gain, rotated key part, zeros] to the tokens' cache rows and returns the queries
     [T, H * dpad] with channels [rank, rank + dr) of every head filled (the rotated parts; channels [0, rank) are left
-    for :func:`headwise_linear`)."""
+    for :func:`headwise_linear`).  ``q_src``: the float32 tensor that holds the queries at ``q_off`` where that is not
+    ``proj`` (queries made by a product of their own).  ``interleaved``: the rotation pairs channel 2j with channel 2j + 1
+    instead of channel c with channel c + dr / 2."""
     _dev(proj, "proj", torch.float32); _dev(block_table, "block_table", torch.int32); _dev(table, "table", torch.float32)
+    q_src = proj if q_src is None else _dev(q_src, "q_src", torch.float32)
+    if q_src.shape[0] != proj.shape[0]:
+        raise KernelError("latent_prep: queries and latent must have the same rows")
     _dev(c_gain, "c_gain", torch.float32); _dev(k_pages, "k_pages")
     T = proj.shape[0]
     num_pages, nkv, page_size, dpad = k_pages.shape
     if nkv != 1 or dpad < rank + dr or tuple(table.shape) != (T, dr) or c_gain.numel() != rank:
         raise KernelError("latent_prep: pages [num_pages, 1, page, >= rank + dr], table [T, dr], gain [rank]")
     q = torch.empty((T, H * dpad), dtype=k_pages.dtype, device=proj.device)
-    fn = _fn("latent", "bw_latent_prep", [c_void_p, c_ll, c_int, c_int] + [c_void_p] * 3 + [c_int, c_void_p, c_void_p, c_float,
-                                          c_void_p, c_void_p] + [c_int] * 9 + [c_void_p])
-    _check(fn(_ptr(proj), proj.stride(0), int(q_off), int(kv_off), _ptr(batch.positions), _ptr(batch.req_of_token),
+    fn = _fn("latent", "bw_latent_prep", [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int] + [c_void_p] * 3 +
+             [c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p] + [c_int] * 9 + [c_void_p])
+    _check(fn(_ptr(q_src), q_src.stride(0), int(q_off), _ptr(proj), proj.stride(0), int(kv_off), int(interleaved),
+              _ptr(batch.positions), _ptr(batch.req_of_token),
               _ptr(block_table), block_table.shape[1], _ptr(table), _ptr(c_gain), float(eps), _ptr(q), _ptr(k_pages),
               _code(k_pages, "pages"), T, H, d, dr, rank, dpad, page_size, num_pages if append else 0, _stream()), "latent_prep")
     return q
@@ -1340,24 +1426,33 @@ def gla_decay(proj: torch.Tensor, x_off: int, w: torch.Tensor, b: torch.Tensor, 
 
 
 def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, batch, state: torch.Tensor,
-             heads: int, dk: int, dv: int, q_scale: float) -> torch.Tensor:
+             heads: int, dk: int, dv: int, q_scale: float, k_scale: Optional[torch.Tensor] = None,
+             scalar_decay: bool = False, ones_col: bool = False) -> torch.Tensor:
     """The recurrence ``S <- diag(a) S + k v^T, o = S^T (q_scale q)`` over the step's tokens, request by request
     in order, from and into ``state`` [slots, heads, dk, dv] (float32) at the requests' slots.  ``proj`` float32
     [T, ld] holds q, k, v at the given column offsets (head-major); ``decay`` float32 [T, heads * dk] holds a
-    (:func:`gla_decay`).  Returns o float32 [T, heads * dv]."""
+    (:func:`gla_decay`).  Returns o float32 [T, heads * dv].  For a memory with one decay per head and a normaliser:
+    ``scalar_decay``: ``decay`` is [T, heads]; ``k_scale`` float32 [T, heads]: the keys are multiplied by it as they are
+    read; ``ones_col``: ``dv`` counts one more value column than ``proj`` holds, the constant 1, so that the state's
+    last column is n <- a n + k and the output's last column n . q."""
     _dev(proj, "proj", torch.float32); _dev(decay, "decay", torch.float32); _dev(state, "state", torch.float32)
     T = proj.shape[0]
     if dk > GLA_MAX_KEY_DIM:
         raise KernelError(f"gla_scan: key size {dk} exceeds {GLA_MAX_KEY_DIM}")
-    if decay.shape != (T, heads * dk) or tuple(state.shape[1:]) != (heads, dk, dv):
-        raise KernelError("gla_scan: decay must be [T, heads * dk], state [slots, heads, dk, dv]")
-    if max(q_off + heads * dk, k_off + heads * dk, v_off + heads * dv) > proj.shape[1]:
+    if decay.shape != (T, heads if scalar_decay else heads * dk) or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelError("gla_scan: decay must be [T, heads * dk] ([T, heads] with scalar_decay), state [slots, heads, dk, dv]")
+    if k_scale is not None:
+        _dev(k_scale, "k_scale", torch.float32)
+        if k_scale.shape != (T, heads):
+            raise KernelError("gla_scan: k_scale must be [T, heads]")
+    if max(q_off + heads * dk, k_off + heads * dk, v_off + heads * (dv - int(ones_col))) > proj.shape[1]:
         raise KernelError("gla_scan: q, k or v lie outside the projection's columns")
     o = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
     fn = _fn("gla", "bw_gla_scan", [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_int, c_int, c_int, c_int, c_float, c_void_p])
+                                    c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p])
     _check(fn(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(batch.cu_q), _ptr(batch.state_slot),
-              _ptr(state), _ptr(o), batch.R, heads, dk, dv, float(q_scale), _stream()), "gla_scan")
+              _ptr(state), _ptr(o), batch.R, heads, dk, dv, float(q_scale), _ptr(k_scale), int(scalar_decay),
+              int(ones_col), _stream()), "gla_scan")
     return o
 
 
@@ -1373,6 +1468,45 @@ def gla_gate(o: torch.Tensor, proj: torch.Tensor, g_off: int, gain: torch.Tensor
                                     c_float, c_void_p])
     _check(fn(_ptr(o), _ptr(proj), proj.stride(0), g_off, _ptr(gain), _ptr(out), _code(out, "out"), T, heads, dv,
               float(eps), _stream()), "gla_gate")
+    return out
+
+
+# ------------------------------------------------------------------ matrix memory with exponential gates
+
+def mlstm_gates(proj: torch.Tensor, i_off: int, f_off: int, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float, batch,
+                m_state: torch.Tensor, heads: int):
+    """The gates of a step's tokens, request by request in order, from and into ``m_state`` [slots, heads] (float32):
+    with i = cap tanh((z_i + b_i) / cap), f = log_sigmoid(cap tanh((z_f + b_f) / cap)) (z at columns ``i_off`` /
+    ``f_off`` of ``proj``, float32) and m <- max(f + m, i): returns a = exp(f + m_before - m), b = exp(i - m),
+    e = exp(-m), each float32 [T, heads]."""
+    _dev(proj, "proj", torch.float32); _dev(bias_i, "bias_i", torch.float32); _dev(bias_f, "bias_f", torch.float32)
+    _dev(m_state, "m_state", torch.float32)
+    T = proj.shape[0]
+    if (bias_i.numel() != heads or bias_f.numel() != heads or m_state.dim() != 2 or m_state.shape[1] != heads
+            or max(i_off, f_off) + heads > proj.shape[1]):
+        raise KernelError("mlstm_gates: biases [heads], m_state [slots, heads], the gates inside the projection")
+    a, b, e = (torch.empty((T, heads), dtype=torch.float32, device=proj.device) for _ in range(3))
+    fn = _fn("mlstm", "bw_mlstm_gates", [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 6 +
+             [c_int, c_int, c_void_p])
+    _check(fn(_ptr(proj), proj.stride(0), int(i_off), int(f_off), _ptr(bias_i), _ptr(bias_f), float(cap), _ptr(batch.cu_q),
+              _ptr(batch.state_slot), _ptr(m_state), _ptr(a), _ptr(b), _ptr(e), batch.R, heads, _stream()), "mlstm_gates")
+    return a, b, e
+
+
+def mlstm_out(o: torch.Tensor, e: torch.Tensor, proj: torch.Tensor, g_off: int, gain: torch.Tensor, heads: int, dv: int,
+              eps: float, out_dtype: torch.dtype, den_eps: float = 1e-6) -> torch.Tensor:
+    """Per token and head, from the scan's output ``o`` float32 [T, heads * (dv + 1)] whose last column per head is
+    n . q: ``u = o[:dv] / (max(|n . q|, e) + den_eps)``, then ``u / rms(u) * gain * sigmoid(g)`` with the gain per channel
+    of all heads (float32 [heads * dv]) and g at column ``g_off`` of ``proj``."""
+    _dev(o, "o", torch.float32); _dev(e, "e", torch.float32); _dev(proj, "proj", torch.float32); _dev(gain, "gain", torch.float32)
+    T = o.shape[0]
+    if o.shape[1] != heads * (dv + 1) or e.shape != (T, heads) or gain.numel() != heads * dv or g_off + heads * dv > proj.shape[1]:
+        raise KernelError("mlstm_out: o [T, heads * (dv + 1)], e [T, heads], gain [heads * dv], the gate inside the projection")
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=o.device)
+    fn = _fn("mlstm", "bw_mlstm_out", [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_float, c_float, c_void_p])
+    _check(fn(_ptr(o), _ptr(e), _ptr(proj), proj.stride(0), int(g_off), _ptr(gain), _ptr(out), _code(out, "out"), T, heads, dv,
+              float(eps), float(den_eps), _stream()), "mlstm_out")
     return out
 
 

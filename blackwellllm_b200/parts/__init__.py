@@ -3,5 +3,5 @@ from .base import (Block, BuildContext, FeedForward, FixedStateRequest, Mixer, N
                    ParamSpec, Part, PositionEncoding, build_block, build_ffn, build_mixer, build_norm,
                    build_position, register_block, register_ffn, register_mixer, register_norm,
                    register_position)
-from . import attention, block, gla, latent_attention, mlp, moe, norm, rope  # noqa: F401  (registers the built-in parts)
+from . import attention, block, gla, latent_attention, mlp, mlstm, moe, norm, rope  # noqa: F401  (registers the built-in parts)
 from .linear import Linear

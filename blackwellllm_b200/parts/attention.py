@@ -32,6 +32,14 @@ root mean square, without a gain, before it is cached: done by the kernel that a
 learned numbers per query head, r1 and r2: r1 ln(1 + r2 (i - j)) is taken off the score of query i and key j inside
 the attention kernels) and ``keep_first`` (with a window, the first so many keys of a sequence stay visible, and
 their pages stay with the request).
+
+And: ``score_softcap`` (the scaled score s becomes cap tanh(s / cap)), ``distance_table_far`` (a learned bias per
+distance and query head, tensor "rel" [rows, heads], added to the capped score; the rows' distances are
+``ops.distance_bucket_table``; at load the table is spread out to one float32 entry per distance and head, which is
+what the kernels read), ``fixed_sink`` (a sink whose score is a constant of the design: the same term in the
+denominator as a learned sink) and ``value_mix`` (the values of every layer that has it, but the first such layer of
+the model, are cached as (1 - lam) v + lam v_first, v_first the first such layer's values of the same token: that
+layer leaves its values of the step in ``batch.extras``, the others read them in the kernel that appends).
 """
 from __future__ import annotations
 
@@ -47,7 +55,7 @@ from .linear import Linear
 _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                   "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
                   "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks", "g": "g_proj.weight",
-                  "r1": "r1", "r2": "r2"}
+                  "r1": "r1", "r2": "r2", "rel": "rel", "vmix": "vmix"}
 
 
 class GQAAttention(Mixer):
@@ -82,17 +90,36 @@ class GQAAttention(Mixer):
         if self.v_eps is not None and self.shares_kv:
             raise ValueError("a mixer that shares another run's keys and values norms no values")
         self.dist = None
+        cap = getattr(spec, "score_softcap", None)
+        self.softcap = float(cap) if cap else None
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError("score_softcap must be > 0")
+        far = getattr(spec, "distance_table_far", None)
+        self.rel_far = float(far) if far is not None else None
+        self.rel_rows = getattr(spec, "distance_table_rows", None)
+        self.rel = None
+        fs = getattr(spec, "fixed_sink", None)
+        self.fixed_sink = float(fs) if fs is not None else None
+        if self.fixed_sink is not None and self.has_sink:
+            raise ValueError("a mixer has a learned sink or a fixed one, not both")
+        self.value_mix = getattr(spec, "value_mix", None)
+        self.lam = None
+        if (self.softcap is not None or self.rel_far is not None) and self.has_dist:
+            raise ValueError("a soft cap or a table of biases by distance does not go with the logarithmic distance bias")
+        if self.value_mix is not None and self.shares_kv:
+            raise ValueError("a mixer that shares another run's keys and values mixes no values")
         self.names = dict(_DEFAULT_NAMES)
         self.names.update(dict(getattr(spec, "names", ()) or ()))
         # head size of the cache and the attention kernels: both sizes fit, in steps the kernels take
         step = 16 if ctx.dtype == torch.bfloat16 else 1
         self.dpad = -(-max(self.hd, self.dv) // step) * step
         self.general = (self.qk_norm_eps is not None or self.dv != self.hd or self.dpad != self.hd or self.norm_per_head
-                        or self.q_temp is not None or self.gated or self.shares_kv or self.v_eps is not None)
+                        or self.q_temp is not None or self.gated or self.shares_kv or self.v_eps is not None
+                        or self.value_mix is not None)
         # the kernel that norms per head also takes rows with a gate's columns behind q, k, v, or without k and v,
         # and norms the values
         self.per_head_route = (self.norm_per_head or self.q_temp is not None or self.shares_kv
-                               or self.v_eps is not None or self.gate_per_head)
+                               or self.v_eps is not None or self.gate_per_head or self.value_mix is not None)
         if self.shares_kv and self.qkv_bias:
             raise ValueError("a mixer that shares another run's keys and values has no key and value biases")
         if self.per_head_route and self.qk_norm_eps is not None and not self.norm_per_head:
@@ -136,6 +163,11 @@ class GQAAttention(Mixer):
         if self.has_dist:
             specs += [ParamSpec(n["r1"], (self.nh,), role="bias", init="bias_normal"),
                       ParamSpec(n["r2"], (self.nh,), role="bias", init="ones")]
+        if self.rel_far is not None:
+            specs.append(ParamSpec(n["rel"], (-1 if self.rel_rows is None else int(self.rel_rows), self.nh), role="bias",
+                                   init="bias_normal"))
+        if self.value_mix is not None:
+            specs.append(ParamSpec(n["vmix"], (), role="bias", init="bias_normal"))
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -143,8 +175,17 @@ class GQAAttention(Mixer):
         parts = [tensors[n["q"]]] + ([] if self.shares_kv else [tensors[n["k"]], tensors[n["v"]]])
         if self.has_sink:
             self.sink = tensors[n["sink"]].float().contiguous()
+        elif self.fixed_sink is not None:
+            self.sink = torch.full((self.nh,), self.fixed_sink, dtype=torch.float32, device=tensors[n["q"]].device)
         if self.has_dist:
             self.dist = torch.stack([tensors[n["r1"]].float(), tensors[n["r2"]].float()]).contiguous()
+        if self.rel_far is not None:
+            # one entry per (head, distance) up to the first distance that takes the table's last row
+            table = tensors[n["rel"]].float()
+            rows_of = ops.distance_bucket_table(int(table.shape[0]), self.rel_far).to(table.device)
+            self.rel = table[rows_of].t().contiguous()
+        if self.value_mix is not None:
+            self.lam = tensors[n["vmix"]].float().reshape(1).contiguous()
         if self.gated:
             if self.per_head_route or self.qk_norm_eps is None:
                 # the gate's rows ride in the q/k/v product; the kernel that follows leaves its columns alone
@@ -181,10 +222,22 @@ class GQAAttention(Mixer):
         else:
             qkv = self.qkv(x, out_dtype=torch.float32)
             if self.per_head_route or (self.gated and self.gate is None):
+                v_mix = None
+                if self.value_mix is not None:
+                    # this step's values of the model's first layer that mixes values: it leaves them, the others read them
+                    v_off = (self.nh + self.nkv) * self.hd
+                    mine = qkv[:, v_off:v_off + self.nkv * self.dv]
+                    first = batch.extras.get("value_mix_first")
+                    if first is None:
+                        batch.extras["value_mix_first"] = mine
+                    elif first.shape != mine.shape:
+                        raise ops.KernelError("value mixing: the layers' values differ in size")
+                    else:
+                        v_mix = (first, self.lam)
                 q = self.position.norm_rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, self.dv, self.q_gain,
                                                      self.k_gain, float(self.qk_norm_eps or 0.0), append=owns_cache,
                                                      per_head=True, q_temp=self.q_temp, has_kv=not self.shares_kv,
-                                                     v_eps=float(self.v_eps or 0.0))
+                                                     v_eps=float(self.v_eps or 0.0), v_mix=v_mix)
             elif self.general:
                 q = self.position.norm_rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, self.dv, self.q_gain,
                                                      self.k_gain, float(self.qk_norm_eps or 0.0), append=owns_cache)
@@ -200,7 +253,7 @@ class GQAAttention(Mixer):
                 gate = (g, self.dv)
         o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group],
                                 self.nh, self.window, self.scale, self.chunk, self.sink, gate, self.dist,
-                                self.keep_first if self.window else 0)
+                                self.keep_first if self.window else 0, self.softcap, self.rel)
         if accumulate:
             self.o.add_to(o, residual)
         elif accumulate is None:

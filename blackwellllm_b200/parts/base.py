@@ -116,14 +116,15 @@ class PositionEncoding(Part):
 
     def norm_rotate_append(self, qkv, batch, cache, nh: int, nkv: int, dq: int, dv: int, q_gain, k_gain, eps: float,
                            append: bool = True, per_head: bool = False, q_temp=None, has_kv: bool = True,
-                           v_eps: float = 0.0) -> torch.Tensor:
+                           v_eps: float = 0.0, v_mix=None) -> torch.Tensor:
         """The general form of :meth:`rotate_append`: qkv [T, nh*dq + nkv*dq + nkv*dv] float32; with gains,
         all query channels of a token (and all its key channels) are RMS-normed together first; the cache's
         head size may exceed dq and dv (the rest is written as zeros).  ``per_head``: every head is normed by
         itself (gains of dq entries, shared by the heads) and qkv may have further columns, which are left
         alone; ``q_temp`` (coef, every): the queries are multiplied by 1 + coef log(1 + n), n the whole periods of ``every`` positions in p + 1;
         ``has_kv=False``: qkv holds queries only and nothing is appended; ``v_eps`` > 0: every value head is divided
-        by sqrt(mean(v^2) + v_eps) before it is written."""
+        by sqrt(mean(v^2) + v_eps) before it is written; ``v_mix`` = (v_first float32 [T, nkv * dv], lam: one float32 number
+        on the device): the values are written as (1 - lam) v + lam v_first (``per_head`` only)."""
         raise NotImplementedError
 
     def fuse_projection(self, weight: torch.Tensor, bias: Optional[torch.Tensor], nh: int, nkv: int, hd: int):

@@ -192,7 +192,12 @@ class ParallelBlock(PreNormBlock):
     ``token_shift`` (a vector s), the mixer reads ``h'_t = h_t + (h_{t-1} - h_t) * s`` (zeros before a sequence's first
     token) and the feed-forward h_t as it is; norm and shift are one kernel, and h of a request's last token is kept in a
     state slot of the block's own between steps (every run of the block has its own).  The two sublayers' sums into the
-    stream may stay open together (``ops.gemm_tc_deferred`` chains them); the next block's norm adds them."""
+    stream may stay open together (``ops.gemm_tc_deferred`` chains them); the next block's norm adds them.
+
+    With the layer's ``ffn_norm`` the feed-forward reads a second norm of the same stream: ``x += mixer(norm1(x)) +
+    ffn(norm2(x))`` (no token shift then).  With the layer's ``layer_scale`` (two vectors s1, s2) the sublayers' outputs
+    are multiplied channel by channel before they are added: ``x += s1 * mixer(..) + s2 * ffn(..)``; both sublayers then
+    write to float32 buffers of their own and one kernel (``ops.scale_add``) makes the sum."""
     takes_pending = True
 
     def __init__(self, layer_spec, hidden_size: int, ctx: BuildContext):
@@ -200,19 +205,26 @@ class ParallelBlock(PreNormBlock):
         self.mixer_norm = build_norm(layer_spec.mixer_norm, hidden_size, ctx)
         self.mixer = build_mixer(layer_spec.mixer, hidden_size, ctx)
         self.ffn = build_ffn(layer_spec.ffn, hidden_size, ctx) if layer_spec.ffn is not None else None
-        self.ffn_norm = None                   # there is one norm
+        self.ffn_norm = None                   # one norm, unless the layer names a second one for the feed-forward
+        self.shift_name = getattr(layer_spec, "token_shift", None)
         if layer_spec.ffn_norm is not None:
-            raise ValueError("the parallel arrangement has one norm (mixer_norm); ffn_norm must be None")
+            if self.shift_name is not None:
+                raise ValueError("the parallel arrangement with a token shift has one norm (mixer_norm); ffn_norm must be None")
+            if self.ffn is not None:
+                self.ffn_norm = build_norm(layer_spec.ffn_norm, hidden_size, ctx)
         self.hidden_size = hidden_size
         self.ctx = ctx
-        self.shift_name = getattr(layer_spec, "token_shift", None)
         self.shift = None
+        self.scale_names = getattr(layer_spec, "layer_scale", None)
+        self.scales = None
         if self.shift_name is not None and not hasattr(self.mixer_norm, "gain_f32"):
             raise ValueError(f"{type(self.mixer_norm).__name__} cannot stand before a token shift (it has no gain_f32)")
 
     def _children(self):
         s = self.spec
         kids = [(s.mixer_norm_prefix, self.mixer_norm), (s.mixer_prefix, self.mixer)]
+        if self.ffn_norm is not None:
+            kids.append((s.ffn_norm_prefix, self.ffn_norm))
         if self.ffn is not None:
             kids.append((s.ffn_prefix, self.ffn))
         return kids
@@ -221,12 +233,21 @@ class ParallelBlock(PreNormBlock):
         out = super().param_specs()
         if self.shift_name is not None:
             out.append(ParamSpec(self.shift_name, (self.hidden_size,), role="bias", init="bias_normal"))
+        if self.scale_names is not None:
+            for k, name in enumerate(self.scale_names[:2]):
+                # (a layer without a feed-forward may still store the second vector: taken and not used)
+                out.append(ParamSpec(name, (self.hidden_size,), role="gain", init="ones", optional=k == 1 and self.ffn is None))
+        if self.ffn is None and self.spec.ffn_norm is not None:     # likewise its second norm's gain
+            out.append(ParamSpec(self.spec.ffn_norm_prefix + getattr(self.spec.ffn_norm, "param", "weight"), (self.hidden_size,),
+                                 role="gain", init="ones", optional=True))
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         super().bind(tensors)
         if self.shift_name is not None:
             self.shift = tensors[self.shift_name].float().contiguous()
+        if self.scale_names is not None:
+            self.scales = [tensors[name].float().contiguous() for name in self.scale_names[:2 if self.ffn is not None else 1]]
 
     def cache_request(self):
         rq = self.mixer.cache_request()
@@ -247,9 +268,22 @@ class ParallelBlock(PreNormBlock):
         else:
             mixer_cache = cache
             h = hs = self._normed(self.mixer_norm, residual)
-        self.mixer.forward(hs, residual, batch, mixer_cache, owns_cache)
-        if self.ffn is not None:
-            self.ffn.forward(h, residual, batch)
+            if self.ffn_norm is not None:      # (the first norm has made any open sum of the stream)
+                h = self.ffn_norm.forward(residual)
+        if self.scales is None:
+            self.mixer.forward(hs, residual, batch, mixer_cache, owns_cache)
+            if self.ffn is not None:
+                self.ffn.forward(h, residual, batch)
+            return
+        # each sublayer writes to a buffer of its own; x += s1 * mixer + s2 * ffn is one kernel
+        ym = torch.empty_like(residual)
+        self.mixer.forward(hs, ym, batch, mixer_cache, owns_cache, accumulate=False)
+        if self.ffn is None:
+            ops.scale_add(residual, ym, self.scales[0])
+            return
+        yf = torch.empty_like(residual)
+        self.ffn.forward(h, yf, batch, accumulate=False)
+        ops.scale_add(residual, ym, self.scales[0], yf, self.scales[1])
 
 
 register_block("parallel", ParallelBlock)

@@ -18,6 +18,11 @@ projection (float32 results); ``ops.latent_prep`` (norm of the latent, rotation 
 rotated parts, append); ``ops.headwise_linear`` with W_uk,h^T on the queries' plain parts and with W_uv,h on the
 attention's output; the output projection into the stream.  The rotation is the rotary encoding part's own table
 (YaRN frequencies and magnitude included); the norm, the angles, the scores and the softmax are float32.
+
+Options of the spec: ``q_rank`` (the queries come through a latent of their own: the first product also makes
+``W_dq x``, an RMS norm with a gain follows, then ``W_uq`` makes the queries); ``output_gate`` (the concatenated heads'
+outputs times ``sigmoid(W_g x)``, W_g's rows riding in the first product; the gate is applied after the per-head value
+product, in place); a rotary encoding that pairs channel 2j with channel 2j + 1.
 """
 from __future__ import annotations
 
@@ -30,7 +35,8 @@ from .base import BuildContext, Mixer, PagedKVRequest, ParamSpec, build_position
 from .linear import Linear
 
 _DEFAULT_NAMES = {"q": "q_proj.weight", "dkv": "kv_a_proj.weight", "dkv_norm": "kv_a_norm.weight", "uk": "k_b_proj.weight",
-                  "uv": "v_b_proj.weight", "o": "o_proj.weight", "sink": "sinks"}
+                  "uv": "v_b_proj.weight", "o": "o_proj.weight", "sink": "sinks", "dq": "q_a_proj.weight",
+                  "dq_norm": "q_a_norm.weight", "uq": "q_b_proj.weight", "g": "g_proj.weight"}
 
 
 class LatentAttention(Mixer):
@@ -60,8 +66,14 @@ class LatentAttention(Mixer):
             if n >= 4:
                 self.heads_per_call = n
         self.position = build_position(spec.position, self.dr, ctx)
-        if getattr(self.position, "rotary_dim", None) != self.dr or getattr(self.position, "interleaved", False):
-            raise ValueError("latent attention turns all rot_dim channels, channel i with channel i + rot_dim / 2")
+        if getattr(self.position, "rotary_dim", None) != self.dr:
+            raise ValueError("latent attention turns all rot_dim channels")
+        self.interleaved = bool(getattr(self.position, "interleaved", False))
+        qr = getattr(spec, "q_rank", None)
+        self.q_rank = int(qr) if qr else None
+        self.gated = bool(getattr(spec, "output_gate", False))
+        self.uq: Linear = None
+        self.q_gain = None
         self.proj: Linear = None
         self.uk_t = self.uv = self.c_gain = self.sink = None
         self.o: Linear = None
@@ -71,7 +83,14 @@ class LatentAttention(Mixer):
 
     def param_specs(self) -> List[ParamSpec]:
         W, n = self.hidden_size, self.names
-        specs = [ParamSpec(n["q"], (self.H * (self.d + self.dr), W)), ParamSpec(n["dkv"], (self.rank + self.dr, W)),
+        if self.q_rank is None:
+            specs = [ParamSpec(n["q"], (self.H * (self.d + self.dr), W))]
+        else:
+            specs = [ParamSpec(n["dq"], (self.q_rank, W)), ParamSpec(n["dq_norm"], (self.q_rank,), role="gain", init="ones"),
+                     ParamSpec(n["uq"], (self.H * (self.d + self.dr), self.q_rank))]
+        if self.gated:
+            specs.append(ParamSpec(n["g"], (self.H * self.dv, W)))
+        specs += [ParamSpec(n["dkv"], (self.rank + self.dr, W)),
                  ParamSpec(n["dkv_norm"], (self.rank,), role="gain", init="ones"),
                  ParamSpec(n["uk"], (self.H * self.d, self.rank)), ParamSpec(n["uv"], (self.H * self.dv, self.rank)),
                  ParamSpec(n["o"], (W, self.H * self.dv))]
@@ -81,7 +100,13 @@ class LatentAttention(Mixer):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
-        self.proj = Linear(torch.cat([tensors[n["q"]], tensors[n["dkv"]]], dim=0))
+        # one product reads the input: [queries or their latent | the keys' and values' latent and rotated part | gate]
+        first = tensors[n["q"]] if self.q_rank is None else tensors[n["dq"]]
+        self.q_cols = first.shape[0]
+        self.proj = Linear(torch.cat([first, tensors[n["dkv"]]] + ([tensors[n["g"]]] if self.gated else []), dim=0))
+        if self.q_rank is not None:
+            self.q_gain = tensors[n["dq_norm"]].contiguous()
+            self.uq = Linear(tensors[n["uq"]])
         self.c_gain = tensors[n["dkv_norm"]].float().contiguous()
         # per head [outputs, inputs]: W_uk,h^T takes head_dim inputs to kv_rank outputs, W_uv,h kv_rank inputs to v_head_dim
         self.uk_t = tensors[n["uk"]].view(self.H, self.d, self.rank).transpose(1, 2).contiguous()
@@ -91,19 +116,28 @@ class LatentAttention(Mixer):
 
     def forward(self, x, residual, batch, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         H, d, dr, rank = self.H, self.d, self.dr, self.rank
-        proj = self.proj(x, out_dtype=torch.float32)       # [T, H * (d + dr) | rank + dr]
+        proj = self.proj(x, out_dtype=torch.float32)       # [T, H * (d + dr) or q_rank | rank + dr | gate]
+        kv_off = self.q_cols
+        if self.q_rank is None:
+            qs = proj
+        else:   # the queries' latent, normed in float32, then the queries themselves (float32 results)
+            cq = ops.rmsnorm(proj[:, :self.q_rank], self.q_gain, self.eps, self.ctx.dtype)
+            qs = self.uq(cq, out_dtype=torch.float32)
         y = torch.empty((x.shape[0], H * self.dv), dtype=x.dtype, device=x.device)
         table, bt = self.position.table(batch), batch.block_tables[cache.group]
         # all heads share the one cached row; the tensor-core kernels stack up to ops.MAX_GROUP_BF16 query heads on a
         # key/value head, so more heads than that run as several groups of heads over the same rows
         n = self.heads_per_call
         for h0 in range(0, H, n):
-            q = ops.latent_prep(proj, h0 * (d + dr), H * (d + dr), batch, bt, table, self.c_gain, self.eps, cache.k_pages,
-                                n, d, dr, rank, append=owns_cache and h0 == 0)
-            ops.headwise_linear(proj, h0 * (d + dr), d + dr, self.uk_t[h0:h0 + n], q, 0, self.dpad)
+            q = ops.latent_prep(proj, h0 * (d + dr), kv_off, batch, bt, table, self.c_gain, self.eps, cache.k_pages,
+                                n, d, dr, rank, append=owns_cache and h0 == 0, q_src=qs, interleaved=self.interleaved)
+            ops.headwise_linear(qs, h0 * (d + dr), d + dr, self.uk_t[h0:h0 + n], q, 0, self.dpad)
             o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, bt, n, self.window, self.scale, None,
                                     None if self.sink is None else self.sink[h0:h0 + n], None)
             ops.headwise_linear(o, 0, self.dpad, self.uv[h0:h0 + n], y, h0 * self.dv, self.dv)
+        if self.gated:
+            g_off = kv_off + rank + dr
+            ops.sigmoid_gate(y, proj[:, g_off:g_off + H * self.dv], H, self.dv)
         if accumulate:
             self.o.add_to(y, residual)
         elif accumulate is None:

@@ -84,11 +84,14 @@ class RotaryEncoding(PositionEncoding):
         return self._table(batch)
 
     def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True,
-                           per_head=False, q_temp=None, has_kv=True, v_eps=0.0):
+                           per_head=False, q_temp=None, has_kv=True, v_eps=0.0, v_mix=None):
+        if v_mix is not None and not per_head:
+            raise ops.KernelError("value mixing goes with the per-head norm's kernel")
         if per_head or q_temp is not None or not has_kv or v_eps:
             return ops.head_norm_rope_append(qkv, batch, batch.block_tables[cache.group], self._table(batch), self.rotary_dim,
                                              self.interleaved, q_gain, k_gain, eps, cache.k_pages, cache.v_pages, nh, nkv,
-                                             dq, dv, has_kv=has_kv, append=append, q_temp=q_temp, v_eps=v_eps)
+                                             dq, dv, has_kv=has_kv, append=append, q_temp=q_temp, v_eps=v_eps,
+                                             v_mix=v_mix)
         return ops.qk_norm_rope_append(qkv, batch, batch.block_tables[cache.group], self._table(batch), self.rotary_dim,
                                        self.interleaved, q_gain, k_gain, eps, cache.k_pages, cache.v_pages, nh, nkv,
                                        dq, dv, append=append)
@@ -151,11 +154,13 @@ class NoPosition(PositionEncoding):
                                None, 0, cache.k_pages, cache.v_pages, nh, nkv, hd, append=append)
 
     def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True,
-                           per_head=False, q_temp=None, has_kv=True, v_eps=0.0):
+                           per_head=False, q_temp=None, has_kv=True, v_eps=0.0, v_mix=None):
+        if v_mix is not None and not per_head:
+            raise ops.KernelError("value mixing goes with the per-head norm's kernel")
         if per_head or q_temp is not None or not has_kv or v_eps:
             return ops.head_norm_rope_append(qkv, batch, batch.block_tables[cache.group], None, 0, False, q_gain, k_gain,
                                              eps, cache.k_pages, cache.v_pages, nh, nkv, dq, dv, has_kv=has_kv,
-                                             append=append, q_temp=q_temp, v_eps=v_eps)
+                                             append=append, q_temp=q_temp, v_eps=v_eps, v_mix=v_mix)
         return ops.qk_norm_rope_append(qkv, batch, batch.block_tables[cache.group], None, 0, False, q_gain, k_gain,
                                        eps, cache.k_pages, cache.v_pages, nh, nkv, dq, dv, append=append)
 
