@@ -29,6 +29,8 @@ def distance_bucket(n, rows, far):
     half = rows // 2
     if n < half:
         return n
+    if half == 0:
+        return 0
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
 
 
