@@ -380,8 +380,34 @@ ZIGIPEL_SHAPES = {
     "2k": (2048, 16, 4, 128, 1024, 4, 16, 128, 64, 128, 192, 5632, 32000, 1, 2),
     "4k": (4096, 32, 8, 128, 1024, 4, 32, 128, 64, 128, 192, 11008, 32000, 1, 2),
 }
+def _vubotar_shape(width, heads, kv, hd, window, keep, m_heads, m_dk, m_dv, l_heads, l_dim, l_rot, l_vdim, l_rank, l_qrank,
+                   experts, top, ff, vocab):
+    """Four layers (matrix memory, attention, latent attention, attention; the two attention layers mix values), each
+    with a routed feed-forward; beside it the dense decoder of equal width, depth, heads and ACTIVE feed-forward size,
+    and the closest design the engine had before: Gafulix with the same heads, the memory's sizes for its gated linear
+    attention, the same experts and the window as its mask block."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0, "bias_max": 4 * window,
+                     "bias_rows": 32, "v_mix": True, "mask": {"size": window, "keep_first": keep}}}
+    mem = {"type": "mlstm", "mlp": moe, "mixer": {"heads": m_heads, "dim": m_dk, "vdim": m_dv, "gate_cap": 12.0}}
+    lat = {"type": "latent_attention", "mlp": moe,
+           "mixer": {"heads": l_heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "kv_rank": l_rank, "q_rank": l_qrank,
+                     "scale": (l_dim + l_rot) ** -0.5, "rot": {"base": 10000.0, "dims": l_rot}}}
+    design = {"architecture": "Vubotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+              "logit_scale": 1.0, "logit_softcap": 30.0, "layers": [mem, att, lat, att]}
+    closest, dense = _gafulix_shape(width, heads, kv, hd, m_heads, m_dk, m_dv, experts, top, ff, window, vocab, 2)
+    return design, dense, {"gafulix": closest}
+
+
+VUBOTAR_SHAPES = {
+    # width, heads, kv heads, head size, window, kept first keys, memory: heads, key size, value size, latent: heads, plain
+    # size, rotated size, value size, rank, query rank, experts, top, expert size, vocab
+    "2k": (2048, 16, 4, 128, 1024, 4, 8, 128, 256, 16, 128, 64, 128, 192, 768, 16, 2, 1024, 32000),
+    "4k": (4096, 32, 8, 128, 1024, 4, 16, 128, 256, 32, 128, 64, 128, 192, 1536, 8, 2, 3584, 32000),
+}
 DESIGNS = {"gafulix": (_gafulix_shape, DESIGN_SHAPES), "fuvevik": (_fuvevik_shape, FUVEVIK_SHAPES),
-           "zigipel": (_zigipel_shape, ZIGIPEL_SHAPES)}
+           "zigipel": (_zigipel_shape, ZIGIPEL_SHAPES), "vubotar": (_vubotar_shape, VUBOTAR_SHAPES)}
 
 
 def design_comparison(args):
@@ -398,10 +424,10 @@ def design_comparison(args):
            "peaks": pk, "sizes": {}}
     gen = torch.Generator().manual_seed(7)
     for key in [k for k in args.design_sizes.split(",") if k]:
-        design, dense = shape_of(*shapes[key])
+        design, dense, *more = shape_of(*shapes[key])     # (a design may name further models to stand beside it)
         V = design["vocab"]
         row = {}
-        for label, cfg in ((args.design, design), ("dense", dense)):
+        for label, cfg in [(args.design, design), ("dense", dense)] + [kv for extra in more for kv in extra.items()]:
             page = 16
             eng = Engine.from_config(cfg, seed=3, std=0.02, dtype="bfloat16", page_size=page,
                                      num_pages=(B + 1) * -(-(max(T, C) + args.steps + args.warmup + 64) // page),

@@ -220,6 +220,40 @@ __global__ void scale_add_kernel(float* __restrict__ x, const float* __restrict_
     }
 }
 
+// The same sum and, in the same pass over the row, two RMS norms of the new row with a gain each (a block whose two
+// sublayers read two norms of the same stream): x[t] += a[t] * ga + b[t] * gb (a == null: x stays as it is), then
+// o1[t] = x[t] / rms(x[t]) * w1 and (o2 != null) o2[t] = x[t] / rms(x[t]) * w2.  One block per row; every thread re-reads
+// only what it wrote itself; the order of the sum of squares depends on H and the block size alone.
+template <typename WT, typename OT>
+__global__ void scale_add_norm2_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ ga,
+                                       const float* __restrict__ b, const float* __restrict__ gb,
+                                       const WT* __restrict__ w1, const WT* __restrict__ w2, OT* __restrict__ o1,
+                                       OT* __restrict__ o2, int H, float eps1, float eps2) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    __shared__ float scratch[32];
+    const size_t row = (size_t)blockIdx.x * H;
+    float* xr = x + row;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = xr[c];
+        if (a) {
+            float y = a[row + c] * ga[c];
+            if (b) y += b[row + c] * gb[c];
+            v += y;
+            xr[c] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = bw::block_sum(ss, scratch) / (float)H;
+    const float r1 = rsqrtf(ss + eps1), r2 = rsqrtf(ss + eps2);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = xr[c];
+        o1[row + c] = bw::from_f32<OT>(v * r1 * bw::to_f32(w1[c]));
+        if (o2) o2[row + c] = bw::from_f32<OT>(v * r2 * bw::to_f32(w2[c]));
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU and other activations
 // in: [T, 2I] with gate in columns [0, I) and up in [I, 2I); out: [T, I] = bw::glu(act, gate, up, limit, alpha)
 // (BW_ACT_SILU: silu(gate) * up).
@@ -600,6 +634,29 @@ BW_EXPORT int bw_scale_add(float* x, const float* a, const float* ga, const floa
     const long long total = (long long)T * H, want = (total + 255) / 256;
     bw::launch(scale_add_kernel, dim3((unsigned)(want < 148 * 8 ? want : 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
                x, a, ga, b, gb, (size_t)total, H);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+// x, a, b: float32 [T, H] (a, or b alone, may be null); ga, gb: float32 [H]; w1, w2: gains of w_type; o1, o2 (o2 may be
+// null): [T, H] of out_type.
+BW_EXPORT int bw_scale_add_norm2(float* x, const float* a, const float* ga, const float* b, const float* gb, const void* w1,
+                                 const void* w2, int w_type, void* o1, void* o2, int out_type, int T, int H, float eps1,
+                                 float eps2, void* stream) {
+    if (T <= 0) return 0;
+    if (!x || !w1 || !o1 || H <= 0 || (a != nullptr) != (ga != nullptr) || (b != nullptr) != (gb != nullptr) || (b && !a) ||
+        (o2 != nullptr) != (w2 != nullptr))
+        return BW_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define BW_SAN(WT, OT) bw::launch((scale_add_norm2_kernel<WT, OT>), dim3(T), dim3(threads), 0, s, x, a, ga, b, gb, \
+        (const WT*)w1, (const WT*)w2, (OT*)o1, (OT*)o2, H, eps1, eps2)
+    if (w_type == BW_F32 && out_type == BW_F32) BW_SAN(float, float);
+    else if (w_type == BW_F32 && out_type == BW_BF16) BW_SAN(float, bf16);
+    else if (w_type == BW_BF16 && out_type == BW_F32) BW_SAN(bf16, float);
+    else if (w_type == BW_BF16 && out_type == BW_BF16) BW_SAN(bf16, bf16);
+    else return BW_ERR_BAD_ARG;
+#undef BW_SAN
     BW_LAUNCH_CHECK();
     return 0;
 }

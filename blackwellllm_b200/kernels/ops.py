@@ -1158,6 +1158,36 @@ def scale_add(stream: torch.Tensor, a: torch.Tensor, ga: torch.Tensor, b: Option
     return stream
 
 
+def scale_add_norm2(stream: torch.Tensor, pending: Optional[tuple], w1: torch.Tensor, eps1: float,
+                    w2: Optional[torch.Tensor], eps2: float, out_dtype: torch.dtype):
+    """One pass over the stream's rows: with ``pending`` = (a, ga, b, gb) (b and gb may be None) first
+    ``stream += a * ga + b * gb`` as :func:`scale_add` makes it, then two RMS norms of the new rows, ``stream / rms *
+    w1`` and (``w2`` given) ``stream / rms * w2``, in ``out_dtype``.  Returns (h1, h2 or None)."""
+    _dev(stream, "stream", torch.float32); _dev(w1, "w1")
+    T, H = stream.shape
+    a = ga = b = gb = None
+    if pending is not None:
+        a, ga, b, gb = pending
+        _dev(a, "a", torch.float32); _dev(ga, "ga", torch.float32)
+        if a.shape != (T, H) or ga.numel() != H or (b is None) != (gb is None):
+            raise KernelError("scale_add_norm2: a (and b) must have the stream's shape, the gains its width")
+        if b is not None:
+            _dev(b, "b", torch.float32); _dev(gb, "gb", torch.float32)
+            if b.shape != (T, H) or gb.numel() != H:
+                raise KernelError("scale_add_norm2: b must have the stream's shape, its gain the width")
+    if w1.numel() != H or (w2 is not None and (w2.numel() != H or w2.dtype != w1.dtype)):
+        raise KernelError("scale_add_norm2: the norms' gains must have the stream's width and one type")
+    h1 = torch.empty((T, H), dtype=out_dtype, device=stream.device)
+    h2 = torch.empty((T, H), dtype=out_dtype, device=stream.device) if w2 is not None else None
+    if w2 is not None:
+        _dev(w2, "w2")
+    fn = _fn("elementwise", "bw_scale_add_norm2", [c_void_p] * 7 + [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                                                  c_float, c_void_p])
+    _check(fn(_ptr(stream), _ptr(a), _ptr(ga), _ptr(b), _ptr(gb), _ptr(w1), _ptr(w2), _code(w1, "w1"), _ptr(h1), _ptr(h2),
+              _code(h1, "out"), T, H, float(eps1), float(eps2), _stream()), "scale_add_norm2")
+    return h1, h2
+
+
 # ------------------------------------------------------------------ q/k norm + rotation + append
 
 def qk_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, table: Optional[torch.Tensor],

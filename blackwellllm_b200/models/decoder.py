@@ -23,7 +23,7 @@ import torch
 from ..config.specs import ModelConfig
 from ..kernels import ops
 from ..parts import BuildContext, FixedStateRequest, ParamSpec, build_block, build_norm
-from ..parts.block import flush_hyper_write
+from ..parts.block import flush_hyper_write, flush_scaled_sum
 from ..parts.linear import Linear
 
 
@@ -150,6 +150,8 @@ class DecoderModel:
             blk = self.blocks[e.layer]
             if not blk.takes_pending or e.add_embedding or e.pass_input is not None:
                 ops.resolve_pending()   # the block before may have left its last sum to the next reader
+            if not getattr(blk, "takes_scaled_sum", False) or e.add_embedding or e.pass_input is not None:
+                flush_scaled_sum(h, batch)   # sublayer outputs that a block left to the stream's next reader
             if e.add_embedding:
                 ops.add_into(h, h0)
             if e.pass_input is not None:
@@ -158,6 +160,7 @@ class DecoderModel:
             blk.forward(h, batch, cache, owns_cache=e.cache_of is None)
             if self.stream_hook is not None:
                 ops.resolve_pending()
+                flush_scaled_sum(h, batch)
                 if S is not None:   # the hook sees the sum of the copies
                     flush_hyper_write(h, batch, S)
                     self.stream_hook(pos, ops.hc_step(h, S, in_w=self._ones))
@@ -167,6 +170,7 @@ class DecoderModel:
         if n == 0:
             ops.discard_pending(h)
             batch.extras.pop("hc_write", None)
+            batch.extras.pop("scaled_sum", None)
             return torch.empty((0, self.config.vocab_size), dtype=torch.float32, device=h.device)
         if S is not None:
             # the last block's write, the sum of the copies and the model's norm, on the wanted rows only
@@ -174,6 +178,9 @@ class DecoderModel:
             x = ops.hc_step(h, S, y, mix, out_w, in_w=self._ones, gain=self.final_norm.gain_f32(), eps=self.final_norm.eps,
                             rows=batch.logit_rows, out_dtype=self.ctx.dtype)
         else:
+            if "scaled_sum" in batch.extras:
+                ops.resolve_pending()
+                flush_scaled_sum(h, batch)
             if not self.final_norm.adds_pending:
                 ops.resolve_pending()
             x = self.final_norm.forward(h, rows=batch.logit_rows)

@@ -108,12 +108,13 @@ def _latent(m: Mapping[str, Any], w: str, eps: float) -> LatentAttentionSpec:
     base = _get(rot, "base", w + ".rot", float)
     if not base > 1:
         raise ConfigError(f"config.json: {w}.rot.base must be > 1, got {base!r}")
-    if m.get("mask") is not None:
-        raise ConfigError(f"config.json: {w}.mask: this mixer sees every earlier key")
+    window, keep = _window(m, w)      # (the design's latent mixer sees every earlier key; a window is taken if one is given)
+    if keep:
+        raise ConfigError(f"config.json: {w}.mask.keep_first: this mixer keeps no first keys")
     return LatentAttentionSpec(num_heads=_get(m, "heads", w, int), head_dim=_get(m, "dim", w, int), rot_dim=rot_dim,
                                v_head_dim=_get(m, "vdim", w, int), kv_rank=_get(m, "kv_rank", w, int), norm_eps=eps,
                                position=RopeSpec(theta=base, rotary_dim=dims, scaling=None, interleaved=True),
-                               softmax_scale=_get(m, "scale", w, float), window=None, sink=False, names=_LATENT_NAMES,
+                               softmax_scale=_get(m, "scale", w, float), window=window, sink=False, names=_LATENT_NAMES,
                                q_rank=_get(m, "q_rank", w, int), output_gate=True)
 
 

@@ -109,7 +109,8 @@ class GQAAttention(Mixer):
         if self.value_mix is not None and self.shares_kv:
             raise ValueError("a mixer that shares another run's keys and values mixes no values")
         self.names = dict(_DEFAULT_NAMES)
-        self.names.update(dict(getattr(spec, "names", ()) or ()))
+        self._given_names = dict(getattr(spec, "names", ()) or ())
+        self.names.update(self._given_names)
         # head size of the cache and the attention kernels: both sizes fit, in steps the kernels take
         step = 16 if ctx.dtype == torch.bfloat16 else 1
         self.dpad = -(-max(self.hd, self.dv) // step) * step
@@ -168,6 +169,9 @@ class GQAAttention(Mixer):
                                    init="bias_normal"))
         if self.value_mix is not None:
             specs.append(ParamSpec(n["vmix"], (), role="bias", init="bias_normal"))
+        elif "vmix" in self._given_names:
+            # a design that has the mixing number may store it in layers that do not mix: taken and not used
+            specs.append(ParamSpec(n["vmix"], (), role="bias", init="bias_normal", optional=True))
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:

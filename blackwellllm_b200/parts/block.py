@@ -197,8 +197,13 @@ class ParallelBlock(PreNormBlock):
     With the layer's ``ffn_norm`` the feed-forward reads a second norm of the same stream: ``x += mixer(norm1(x)) +
     ffn(norm2(x))`` (no token shift then).  With the layer's ``layer_scale`` (two vectors s1, s2) the sublayers' outputs
     are multiplied channel by channel before they are added: ``x += s1 * mixer(..) + s2 * ffn(..)``; both sublayers then
-    write to float32 buffers of their own and one kernel (``ops.scale_add``) makes the sum."""
+    write to float32 buffers of their own, and the sum is left to whoever reads the stream next
+    (``batch.extras["scaled_sum"]`` holds the buffers and vectors until then): the next such block makes it inside the
+    kernel that norms the new rows (``ops.scale_add_norm2``: the sum and both norms in one pass over the stream); anyone
+    else calls :func:`flush_scaled_sum` first (the decoder does, before a block of another kind, before the model's last
+    norm and before it hands the stream out)."""
     takes_pending = True
+    takes_scaled_sum = True
 
     def __init__(self, layer_spec, hidden_size: int, ctx: BuildContext):
         self.spec = layer_spec
@@ -217,6 +222,11 @@ class ParallelBlock(PreNormBlock):
         self.shift = None
         self.scale_names = getattr(layer_spec, "layer_scale", None)
         self.scales = None
+        # both norms plain RMS norms (a gain, no offset, nothing else): one kernel makes them, and the block before's sum
+        from .norm import RMSNorm
+        self._fused_norms = (self.shift_name is None and type(self.mixer_norm) is RMSNorm and self.mixer_norm.offset == 0.0
+                             and (self.ffn_norm is None or (type(self.ffn_norm) is RMSNorm and self.ffn_norm.offset == 0.0))
+                             and (self.scale_names is not None or self.ffn_norm is not None))
         if self.shift_name is not None and not hasattr(self.mixer_norm, "gain_f32"):
             raise ValueError(f"{type(self.mixer_norm).__name__} cannot stand before a token shift (it has no gain_f32)")
 
@@ -248,6 +258,8 @@ class ParallelBlock(PreNormBlock):
             self.shift = tensors[self.shift_name].float().contiguous()
         if self.scale_names is not None:
             self.scales = [tensors[name].float().contiguous() for name in self.scale_names[:2 if self.ffn is not None else 1]]
+        if self._fused_norms and self.ffn_norm is not None and self.ffn_norm.weight.dtype != self.mixer_norm.weight.dtype:
+            self._fused_norms = False     # gains stored in different types: each norm runs by itself
 
     def cache_request(self):
         rq = self.mixer.cache_request()
@@ -265,8 +277,16 @@ class ParallelBlock(PreNormBlock):
             mixer_cache, state = (cache[0], cache[1]) if len(cache) == 2 else (None, cache[0])
             h, hs = ops.rmsnorm_shift(residual, self.mixer_norm.gain_f32(), self.shift, state.state, batch,
                                       self.mixer_norm.eps, self.ctx.dtype, want_h=self.ffn is not None)
+        elif self._fused_norms:
+            # the sum that the block before left, and both norms of the new rows, in one pass over the stream
+            mixer_cache = cache
+            ops.resolve_pending()
+            n1, n2 = self.mixer_norm, self.ffn_norm
+            hs, h = ops.scale_add_norm2(residual, batch.extras.pop("scaled_sum", None), n1.weight, n1.eps,
+                                        None if n2 is None else n2.weight, 0.0 if n2 is None else n2.eps, self.ctx.dtype)
         else:
             mixer_cache = cache
+            flush_scaled_sum(residual, batch)
             h = hs = self._normed(self.mixer_norm, residual)
             if self.ffn_norm is not None:      # (the first norm has made any open sum of the stream)
                 h = self.ffn_norm.forward(residual)
@@ -278,12 +298,18 @@ class ParallelBlock(PreNormBlock):
         # each sublayer writes to a buffer of its own; x += s1 * mixer + s2 * ffn is one kernel
         ym = torch.empty_like(residual)
         self.mixer.forward(hs, ym, batch, mixer_cache, owns_cache, accumulate=False)
-        if self.ffn is None:
-            ops.scale_add(residual, ym, self.scales[0])
-            return
-        yf = torch.empty_like(residual)
-        self.ffn.forward(h, yf, batch, accumulate=False)
-        ops.scale_add(residual, ym, self.scales[0], yf, self.scales[1])
+        yf = None
+        if self.ffn is not None:
+            yf = torch.empty_like(residual)
+            self.ffn.forward(h, yf, batch, accumulate=False)
+        batch.extras["scaled_sum"] = (ym, self.scales[0], yf, None if yf is None else self.scales[1])
+
+
+def flush_scaled_sum(residual, batch) -> None:
+    """Makes the sum that a block with a layer scale left open, so that ``residual`` holds the stream as it is."""
+    pend = batch.extras.pop("scaled_sum", None)
+    if pend is not None:
+        ops.scale_add(residual, *pend)
 
 
 register_block("parallel", ParallelBlock)

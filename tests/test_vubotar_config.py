@@ -102,7 +102,7 @@ def test_what_the_layers_ask_of_the_cache():
     (lambda r: r["layers"][0]["mlp"].__setitem__("kind", "dense"), "not a feed-forward"),
     (lambda r: r["layers"][1]["mixer"].__setitem__("kv_heads", 4), "multiple"),
     (lambda r: r["layers"][2]["mixer"]["rot"].__setitem__("dims", 6), "rot_dim"),
-    (lambda r: r["layers"][2]["mixer"].__setitem__("mask", {"size": 4}), "every earlier key"),
+    (lambda r: r["layers"][2]["mixer"].__setitem__("mask", {"size": 4, "keep_first": 2}), "keeps no first keys"),
     (lambda r: r["layers"][3]["mixer"].__setitem__("vdim", 8), "other kv_heads or vdim"),
     (lambda r: r["layers"][0]["mixer"].__setitem__("gate_cap", 0.0), "> 0"),
     (lambda r: r["layers"][1]["mixer"].__setitem__("softcap", -1.0), "> 0"),

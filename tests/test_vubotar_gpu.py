@@ -54,6 +54,28 @@ def test_layer_scale_sum(ops, T, H):
     assert float((got.double() - (x.double() + a.double() * ga.double())).abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H", [(1, 64), (7, 50), (130, 2048), (3, 4100)])
+def test_layer_scale_sum_and_both_norms_in_one_pass(ops, out_dtype, T, H):
+    x, a, b = rnd(T, H, seed=1), rnd(T, H, seed=2), rnd(T, H, seed=3)
+    ga, gb, w1, w2 = rnd(H, seed=4), rnd(H, seed=5), 1.0 + 0.3 * rnd(H, seed=6), 1.0 + 0.3 * rnd(H, seed=7)
+    tol = 1e-5 if out_dtype == torch.float32 else 2e-2
+    for pending, two in ((True, True), (True, False), (False, True), ("one", True)):
+        xs = d(x.clone())
+        want_x = x.double()
+        pend = None
+        if pending == "one":
+            pend, want_x = (d(a), d(ga), None, None), want_x + a.double() * ga.double()
+        elif pending:
+            pend, want_x = (d(a), d(ga), d(b), d(gb)), want_x + (a.double() * ga.double() + b.double() * gb.double())
+        h1, h2 = ops.scale_add_norm2(xs, pend, d(w1), 1e-5, d(w2) if two else None, 1e-3, out_dtype)
+        assert float((xs.double().cpu() - want_x).abs().max()) < 1e-5
+        assert float((h1.double().cpu() - plain.rms_norm(want_x, w1.double(), 1e-5)).abs().max()) < tol * 4
+        assert (h2 is None) == (not two)
+        if two:
+            assert float((h2.double().cpu() - plain.rms_norm(want_x, w2.double(), 1e-3)).abs().max()) < tol * 4
+
+
 @pytest.mark.parametrize("T,H,ld", [(5, 24, 100), (40, 128, 131), (3, 64, 64)])
 def test_norm_of_a_range_of_columns(ops, T, H, ld):
     wide = rnd(T, ld, seed=7)
