@@ -47,6 +47,7 @@ struct ScanParams {
     // column of the state is n_t = a_t n_(t-1) + k_t and the last output column is n_t . q_t.
     const float* k_scale;
     int scalar_decay, ones_col;
+    int sld;               // floats between the state's rows (>= dv; columns from dv on stay zero)
 };
 
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -96,19 +97,19 @@ gla_scan_kernel(ScanParams p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int cbase = c0 + warp * CPT;
     const int t0 = p.cu_q[r], t1 = p.cu_q[r + 1];
-    float* S = p.state + (((size_t)p.state_slot[r] * p.heads + h) * p.dk) * p.dv;
+    float* S = p.state + (((size_t)p.state_slot[r] * p.heads + h) * p.dk) * p.sld;
     BW_PDL_WAIT();
     float s[RPL][CPT];
-    const bool vec_state = (p.dv & 3) == 0 && cbase + CPT <= p.dv;   // a lane's CPT columns of a row as one 16-byte access
+    const bool vec_state = (p.sld & 3) == 0 && cbase + CPT <= p.sld;   // a lane's CPT columns of a row as one 16-byte access
 #pragma unroll
     for (int j = 0; j < RPL; ++j) {
         const int i = ((j >> 2) * 32 + lane) * 4 + (j & 3);
         if (vec_state) {
-            const float4 v = i < p.dk ? *reinterpret_cast<const float4*>(S + (size_t)i * p.dv + cbase) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 v = i < p.dk ? *reinterpret_cast<const float4*>(S + (size_t)i * p.sld + cbase) : make_float4(0.f, 0.f, 0.f, 0.f);
             s[j][0] = v.x; s[j][1] = v.y; s[j][2] = v.z; s[j][3] = v.w;
         } else {
 #pragma unroll
-            for (int cc = 0; cc < CPT; ++cc) s[j][cc] = (i < p.dk && cbase + cc < p.dv) ? S[(size_t)i * p.dv + cbase + cc] : 0.f;
+            for (int cc = 0; cc < CPT; ++cc) s[j][cc] = (i < p.dk && cbase + cc < p.dv) ? S[(size_t)i * p.sld + cbase + cc] : 0.f;
         }
     }
     // The next chunk's values travel from memory into registers while this chunk is worked on from shared
@@ -190,11 +191,11 @@ gla_scan_kernel(ScanParams p) {
     for (int j = 0; j < RPL; ++j) {
         const int i = ((j >> 2) * 32 + lane) * 4 + (j & 3);
         if (vec_state) {
-            if (i < p.dk) *reinterpret_cast<float4*>(S + (size_t)i * p.dv + cbase) = make_float4(s[j][0], s[j][1], s[j][2], s[j][3]);
+            if (i < p.dk) *reinterpret_cast<float4*>(S + (size_t)i * p.sld + cbase) = make_float4(s[j][0], s[j][1], s[j][2], s[j][3]);
         } else {
 #pragma unroll
             for (int cc = 0; cc < CPT; ++cc)
-                if (i < p.dk && cbase + cc < p.dv) S[(size_t)i * p.dv + cbase + cc] = s[j][cc];
+                if (i < p.dk && cbase + cc < p.dv) S[(size_t)i * p.sld + cbase + cc] = s[j][cc];
         }
     }
 }
@@ -227,18 +228,20 @@ gla_gate_kernel(const float* __restrict__ o, const float* __restrict__ g, long l
 }  // namespace
 
 // decay: float32 [T, heads * dk] from bw_gla_decay; with scalar_decay [T, heads].  k_scale: float32 [T, heads] or null.
-// ones_col != 0: dv counts a last column of ones that v does not hold (state [slots, heads, dk, dv], o [T, heads * dv]).
+// ones_col != 0: dv counts a last column of ones that v does not hold (state [slots, heads, dk, state_ld], o [T, heads * dv]).
+// state_ld: floats between the state's rows (0: dv); with a multiple of 4 a lane moves its columns of a row in one access.
 BW_EXPORT int bw_gla_scan(const float* qkv, long long ld, int q_off, int k_off, int v_off, const float* decay,
                           const int* cu_q, const int* state_slot, float* state, float* o, int R, int heads, int dk,
-                          int dv, float q_scale, const float* k_scale, int scalar_decay, int ones_col, void* stream) {
+                          int dv, float q_scale, const float* k_scale, int scalar_decay, int ones_col, int state_ld,
+                          void* stream) {
     if (R <= 0) return 0;
-    if (heads <= 0 || dk <= 0 || dv <= 0 || (ones_col && dv < 2)) return BW_ERR_BAD_ARG;
+    if (heads <= 0 || dk <= 0 || dv <= 0 || (ones_col && dv < 2) || (state_ld != 0 && state_ld < dv)) return BW_ERR_BAD_ARG;
     if (dk > MAX_DK) return BW_ERR_UNSUPPORTED;
     ScanParams p;
     p.qkv = qkv; p.decay = decay; p.cu_q = cu_q; p.state_slot = state_slot; p.state = state; p.o = o; p.ld = ld;
     p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.heads = heads; p.dk = dk; p.dv = dv;
     p.q_scale = q_scale;
-    p.k_scale = k_scale; p.scalar_decay = scalar_decay; p.ones_col = ones_col;
+    p.k_scale = k_scale; p.scalar_decay = scalar_decay; p.ones_col = ones_col; p.sld = state_ld ? state_ld : dv;
     const dim3 grid(R, heads, (dv + COLS - 1) / COLS);
     const int rpl = dk <= 128 ? 4 : 8;
     const size_t smem = (size_t)(3 * TOK_CHUNK * 32 * rpl + TOK_CHUNK * COLS) * sizeof(float);

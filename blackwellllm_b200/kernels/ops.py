@@ -1464,13 +1464,15 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     (:func:`gla_decay`).  Returns o float32 [T, heads * dv].  For a memory with one decay per head and a normaliser:
     ``scalar_decay``: ``decay`` is [T, heads]; ``k_scale`` float32 [T, heads]: the keys are multiplied by it as they are
     read; ``ones_col``: ``dv`` counts one more value column than ``proj`` holds, the constant 1, so that the state's
-    last column is n <- a n + k and the output's last column n . q."""
+    last column is n <- a n + k and the output's last column n . q.  The state's rows may be longer than ``dv`` (padding that
+    stays zero): with a length that is a multiple of 4 the kernel moves a lane's columns of a row in one access."""
     _dev(proj, "proj", torch.float32); _dev(decay, "decay", torch.float32); _dev(state, "state", torch.float32)
     T = proj.shape[0]
     if dk > GLA_MAX_KEY_DIM:
         raise KernelError(f"gla_scan: key size {dk} exceeds {GLA_MAX_KEY_DIM}")
-    if decay.shape != (T, heads if scalar_decay else heads * dk) or tuple(state.shape[1:]) != (heads, dk, dv):
-        raise KernelError("gla_scan: decay must be [T, heads * dk] ([T, heads] with scalar_decay), state [slots, heads, dk, dv]")
+    if (decay.shape != (T, heads if scalar_decay else heads * dk) or state.dim() != 4 or tuple(state.shape[1:3]) != (heads, dk)
+            or state.shape[3] < dv):
+        raise KernelError("gla_scan: decay must be [T, heads * dk] ([T, heads] with scalar_decay), state [slots, heads, dk, >= dv]")
     if k_scale is not None:
         _dev(k_scale, "k_scale", torch.float32)
         if k_scale.shape != (T, heads):
@@ -1479,10 +1481,10 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
         raise KernelError("gla_scan: q, k or v lie outside the projection's columns")
     o = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
     fn = _fn("gla", "bw_gla_scan", [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p])
+                                    c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(batch.cu_q), _ptr(batch.state_slot),
               _ptr(state), _ptr(o), batch.R, heads, dk, dv, float(q_scale), _ptr(k_scale), int(scalar_decay),
-              int(ones_col), _stream()), "gla_scan")
+              int(ones_col), int(state.shape[3]), _stream()), "gla_scan")
     return o
 
 

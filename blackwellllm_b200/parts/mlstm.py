@@ -8,7 +8,8 @@
     o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
     y = W_o (concat_heads(o / rms(o)) * gain * sigmoid(W_g x))          gain: one entry per channel of all heads
 
-The state (S and n as one [key_dim, value_dim + 1] matrix per head whose last column is n, and m) is float32, lives in the
+The state (S and n as one [key_dim, value_dim + 1] matrix per head whose last column is n, its rows padded to a multiple
+of four floats, and m) is float32, lives in the
 request's slots of the cache manager's fixed-size state (zeroed when the slot is handed out, which is where S, n and m
 start) and is carried from step to step.  q, k, v, the output gate and the two gates' projections are one matrix made at
 load; their results are float32.  Three kernels follow: the gates (``ops.mlstm_gates``: cap, logarithm, the chain of
@@ -50,8 +51,9 @@ class MatrixLSTM(Mixer):
         self.gain = self.bias_i = self.bias_f = None
 
     def cache_request(self):
-        # [S | n] per head, and the running maximum m per head
-        return (FixedStateRequest((self.heads, self.dk, self.dv + 1), torch.float32),
+        # [S | n] per head (rows padded to a multiple of four floats: the scan moves them in 16-byte pieces), and the
+        # running maximum m per head
+        return (FixedStateRequest((self.heads, self.dk, -(-(self.dv + 1) // 4) * 4), torch.float32),
                 FixedStateRequest((self.heads,), torch.float32))
 
     def param_specs(self) -> List[ParamSpec]:

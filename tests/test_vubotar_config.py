@@ -88,7 +88,7 @@ def test_what_the_layers_ask_of_the_cache():
     from blackwellllm_b200.parts import BuildContext, FixedStateRequest, PagedKVRequest
     model = DecoderModel(parse_config(tv.MIXED), BuildContext(torch.device("cpu"), torch.float32))
     rq = model.cache_requests()
-    assert rq[0] == (FixedStateRequest((2, 16, 25), torch.float32), FixedStateRequest((2,), torch.float32))
+    assert rq[0] == (FixedStateRequest((2, 16, 28), torch.float32), FixedStateRequest((2,), torch.float32))
     assert rq[1] == PagedKVRequest(2, 32, 24, 20) and rq[3] == PagedKVRequest(2, 16, 9, 0)
     assert rq[2] == PagedKVRequest(1, 48, None, 0, single_plane=True)
     model16 = DecoderModel(parse_config(tv.OPEN), BuildContext(torch.device("cpu"), torch.bfloat16))

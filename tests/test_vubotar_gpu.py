@@ -259,7 +259,7 @@ def test_matrix_memory_across_steps_and_slots(ops, heads, dk, dv, cap):
                                       xd[:, 2 * K:2 * K + V].view(L, heads, dv), xd[:, 2 * K + 2 * V:2 * K + 2 * V + heads],
                                       xd[:, 2 * K + 2 * V + heads:], bi.double(), bf.double(), cap, 1e-5, gain.double(),
                                       xd[:, 2 * K + V:2 * K + 2 * V]))
-    memory = torch.zeros(4, heads, dk, dv + 1, device=DEV)
+    memory = torch.zeros(4, heads, dk, -(-(dv + 1) // 4) * 4, device=DEV)     # rows padded as the mixer asks for them
     maxima = torch.zeros(4, heads, device=DEV)
     memory[1] = float("nan")            # a slot nobody owns
     at = [0, 0, 0]
