@@ -252,7 +252,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const bool mod = p.softcap > 0.f || p.rel != nullptr;
         const float* rel_row = (p.rel && row_ok) ? p.rel + (size_t)(g * p.G + hg) * p.rel_len : nullptr;
         const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
-        const float sc = (p.dist || mod) ? 1.f : p.scale_log2;   // what turns a kept score into a power of two
+        // what turns a kept score into a power of two
+        const float sc = p.dist ? 1.f : (mod ? 1.4426950408889634f : p.scale_log2);
 
         for (int i = 0; i < n_tiles; ++i) {
             if (!__all_sync(0xffffffffu, bw::mbar_wait(s_full + 8 * (i & 1), (i >> 1) & 1, &g_status, 16))) { ok = false; break; }
@@ -278,15 +279,46 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
             }
             if (mod) {
-                // (uniform over the launch) the scores capped, the table's entry of the distance added, in powers of two
+                // (uniform over the launch) the scores in natural units: scaled, capped, the table's entry of the distance
+                // added; sc turns them into powers of two afterwards
                 const float scale = p.scale_log2 * 0.6931471805599453f;
-                const int d0 = qpos - key0;
+                if (p.softcap > 0.f) {
+                    // cap tanh(s / cap) = s * (tanh(x) / x), x = s / cap: where every x of the warp's 32 rows lies within
+                    // [-1, 1] the polynomial serves (the usual case: a cap well above the scores); else the exponential
+                    const float to_x = scale * inv_cap;
+                    float ax = 0.f;
 #pragma unroll
-                for (int c = 0; c < BN; ++c) {
-                    float x = __uint_as_float(v[c]) * scale;
-                    if (p.softcap > 0.f) x = bw::soft_cap_fast(x, p.softcap, inv_cap);
-                    if (rel_row) x += bw::table_bias(rel_row, p.rel_len, d0 - c > 0 ? d0 - c : 0);
-                    v[c] = __float_as_uint(x * 1.4426950408889634f);
+                    for (int c = 0; c < BN; ++c) ax = fmaxf(ax, fabsf(__uint_as_float(v[c])));
+                    if (__all_sync(0xffffffffu, ax * to_x <= 1.f)) {
+#pragma unroll
+                        for (int c = 0; c < BN; ++c) {
+                            const float x = __uint_as_float(v[c]) * to_x;
+                            v[c] = __float_as_uint(__uint_as_float(v[c]) * scale * bw::tanh_over_x_poly(x * x));
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN; ++c)
+                            v[c] = __float_as_uint(bw::soft_cap_fast(__uint_as_float(v[c]) * scale, p.softcap, inv_cap));
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < BN; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * scale);
+                }
+                if (rel_row) {
+                    const int d0 = qpos - key0;     // the distance of the tile's first key; key c lies at d0 - c
+                    if (d0 >= BN - 1 && d0 < p.rel_len) {          // every distance has its own entry: fixed offsets
+                        const float* tp = rel_row + d0;
+#pragma unroll
+                        for (int c = 0; c < BN; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + tp[-c]);
+                    } else if (d0 - (BN - 1) >= p.rel_len - 1) {   // every key lies beyond the table: its last entry
+                        const float far = rel_row[p.rel_len - 1];
+#pragma unroll
+                        for (int c = 0; c < BN; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) + far);
+                    } else {                                       // the tile of the row's own position, or the table's end
+#pragma unroll
+                        for (int c = 0; c < BN; ++c)
+                            v[c] = __float_as_uint(__uint_as_float(v[c]) + bw::table_bias(rel_row, p.rel_len, d0 - c > 0 ? d0 - c : 0));
+                    }
                 }
             }
             if (need_mask) {   // one branch per tile, not one per key

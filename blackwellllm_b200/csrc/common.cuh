@@ -140,6 +140,17 @@ __device__ __forceinline__ float soft_cap_fast(float s, float cap, float inv_cap
     return cap * (1.f - __fdividef(2.f, e + 1.f));
 }
 
+// tanh(x) / x for |x| <= 1 as a polynomial of degree 5 in x^2 (six coefficients fitted over [0, 1]; the error of x * p is
+// below 6e-7): five FMAs in place of two special-function instructions.
+__device__ __forceinline__ float tanh_over_x_poly(float x2) {
+    float p = -0.0030804092530161142f;
+    p = fmaf(p, x2, 0.01677677594125271f);
+    p = fmaf(p, x2, -0.05163545906543732f);
+    p = fmaf(p, x2, 0.13282513618469238f);
+    p = fmaf(p, x2, -0.33329179883003235f);
+    return fmaf(p, x2, 0.999999463558197f);
+}
+
 // A learned bias per (query head, distance): table float32 [heads][len], the last entry standing for every distance
 // from len - 1 on.
 __device__ __forceinline__ float table_bias(const float* __restrict__ head_row, int len, int dist) {
