@@ -81,7 +81,10 @@ gla_decay_kernel(const float* __restrict__ x, long long ldx, int x_off, const WT
 // and used for CPT columns.  In shared memory a token's rows are padded with zeros to DKP = 32 * RPL channels
 // (a padded channel stays at zero and adds nothing), so the inner loop has no bounds.  The CPT sums over the
 // 32 lanes take six shuffles: two that halve the number of columns a lane carries, then three over what is left.
-template <int RPL>
+// MEM: the form for a matrix memory (ScanParams: one decay per head, keys times k_scale, the column of ones); the plain
+// form's code does not know of it.  What a fetch loads is not touched before it is staged: a thread never waits for a
+// load inside the fetch, so the key's scale travels in registers of its own and multiplies at staging.
+template <int RPL, bool MEM>
 __global__ void __launch_bounds__(THREADS)
 gla_scan_kernel(ScanParams p) {
     BW_PDL_TRIGGER();
@@ -115,28 +118,34 @@ gla_scan_kernel(ScanParams p) {
     // The next chunk's values travel from memory into registers while this chunk is worked on from shared
     // memory, so that their latency is not added to the chain through the tokens.
     float rq[NST], rk[NST], ra[NST], rv[NSV];
+    float rs[MEM ? NST : 1];
+    const int dv_in = p.dv - ((MEM && p.ones_col) ? 1 : 0);   // value columns a head has in memory
     auto fetch = [&](int tb, int n) {
 #pragma unroll
         for (int u = 0; u < NST; ++u) {
             const int idx = threadIdx.x + u * THREADS;
             const int tt = idx / DKP, i = idx % DKP;
             rq[u] = rk[u] = ra[u] = 0.f;
+            if constexpr (MEM) rs[u] = 1.f;
             if (tt < n && i < p.dk) {
                 const float* row = p.qkv + (size_t)(tb + tt) * p.ld;
                 rq[u] = row[p.q_off + h * p.dk + i];
                 rk[u] = row[p.k_off + h * p.dk + i];
-                if (p.k_scale) rk[u] *= p.k_scale[(size_t)(tb + tt) * p.heads + h];
-                ra[u] = p.scalar_decay ? p.decay[(size_t)(tb + tt) * p.heads + h]
-                                       : p.decay[(size_t)(tb + tt) * p.heads * p.dk + h * p.dk + i];
+                if constexpr (MEM) {
+                    if (p.k_scale) rs[u] = p.k_scale[(size_t)(tb + tt) * p.heads + h];
+                    ra[u] = p.scalar_decay ? p.decay[(size_t)(tb + tt) * p.heads + h]
+                                           : p.decay[(size_t)(tb + tt) * p.heads * p.dk + h * p.dk + i];
+                } else {
+                    ra[u] = p.decay[(size_t)(tb + tt) * p.heads * p.dk + h * p.dk + i];
+                }
             }
         }
-        const int dv_in = p.dv - (p.ones_col ? 1 : 0);   // value columns a head has in memory
 #pragma unroll
         for (int u = 0; u < NSV; ++u) {
             const int idx = threadIdx.x + u * THREADS;
             const int tt = idx / COLS, cc = idx % COLS;
             rv[u] = (tt < n && c0 + cc < dv_in) ? p.qkv[(size_t)(tb + tt) * p.ld + p.v_off + h * dv_in + c0 + cc]
-                                                : ((tt < n && p.ones_col && c0 + cc == dv_in) ? 1.f : 0.f);
+                                                : ((MEM && tt < n && p.ones_col && c0 + cc == dv_in) ? 1.f : 0.f);
         }
     };
     if (t0 < t1) fetch(t0, min(TOK_CHUNK, t1 - t0));
@@ -152,7 +161,8 @@ gla_scan_kernel(ScanParams p) {
 #pragma unroll
         for (int u = 0; u < NST; ++u) {
             const int idx = threadIdx.x + u * THREADS;
-            qs[idx] = rq[u] * p.q_scale; ks[idx] = rk[u]; as[idx] = ra[u];
+            qs[idx] = rq[u] * p.q_scale; as[idx] = ra[u];
+            if constexpr (MEM) ks[idx] = rk[u] * rs[u]; else ks[idx] = rk[u];
         }
 #pragma unroll
         for (int u = 0; u < NSV; ++u) vs[threadIdx.x + u * THREADS] = rv[u];
@@ -246,11 +256,19 @@ BW_EXPORT int bw_gla_scan(const float* qkv, long long ld, int q_off, int k_off, 
     const int rpl = dk <= 128 ? 4 : 8;
     const size_t smem = (size_t)(3 * TOK_CHUNK * 32 * rpl + TOK_CHUNK * COLS) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (rpl == 4) bw::launch((gla_scan_kernel<4>), grid, dim3(THREADS), smem, s, p);
-    else {
-        static bool raised[bw::MAX_DEVICES] = {};
-        if (bw::allow_dynamic_smem(gla_scan_kernel<8>, (int)smem, raised) != cudaSuccess) return BW_ERR_DRIVER;
-        bw::launch((gla_scan_kernel<8>), grid, dim3(THREADS), smem, s, p);
+    const bool mem = k_scale || scalar_decay || ones_col;
+    if (rpl == 4) {
+        if (mem) bw::launch((gla_scan_kernel<4, true>), grid, dim3(THREADS), smem, s, p);
+        else bw::launch((gla_scan_kernel<4, false>), grid, dim3(THREADS), smem, s, p);
+    } else {
+        static bool raised[bw::MAX_DEVICES] = {}, raised_mem[bw::MAX_DEVICES] = {};
+        if (mem) {
+            if (bw::allow_dynamic_smem(gla_scan_kernel<8, true>, (int)smem, raised_mem) != cudaSuccess) return BW_ERR_DRIVER;
+            bw::launch((gla_scan_kernel<8, true>), grid, dim3(THREADS), smem, s, p);
+        } else {
+            if (bw::allow_dynamic_smem(gla_scan_kernel<8, false>, (int)smem, raised) != cudaSuccess) return BW_ERR_DRIVER;
+            bw::launch((gla_scan_kernel<8, false>), grid, dim3(THREADS), smem, s, p);
+        }
     }
     BW_LAUNCH_CHECK();
     return 0;

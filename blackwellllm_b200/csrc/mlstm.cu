@@ -19,53 +19,58 @@ namespace {
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-// One warp per (request, head).  A lane takes a token of a stretch of 32: its two gates (the transcendental part, side by
-// side) go to shared memory; then the chain m_t = max(f_t + m_(t-1), i_t) runs through the 32 tokens in order on every lane
-// (an addition and a maximum a token, the gates read as broadcasts that do not wait for the chain), each lane keeping the m
-// before and after its own token; then the lane's three exponentials.  The chain's order is the tokens' order, so the
-// result does not depend on how the tokens were cut into steps.
-constexpr int GATE_WARPS = 4;
-__global__ void __launch_bounds__(GATE_WARPS * 32)
+// One block per (request, head).  First all its warps make the two gates of the segment's tokens (the transcendental
+// part, a token a thread) and park them in the a and b outputs; then warp 0 walks the segment in stretches of 32 tokens:
+// the stretch's gates go to shared memory, the chain m_t = max(f_t + m_(t-1), i_t) runs through them in order on every
+// lane (an addition and a maximum a token, the gates read as broadcasts that do not wait for the chain), each lane keeping
+// the m before and after its own token, then the lane's three exponentials.  The chain's order is the tokens' order, so
+// the result does not depend on how the tokens were cut into steps.
+constexpr int GATE_THREADS = 256;
+__global__ void __launch_bounds__(GATE_THREADS)
 mlstm_gates_kernel(const float* __restrict__ proj, long long ld, int i_off, int f_off, const float* __restrict__ bias_i,
                    const float* __restrict__ bias_f, float cap, const int* __restrict__ cu_q,
-                   const int* __restrict__ state_slot, float* __restrict__ m_state, float* __restrict__ a_out,
-                   float* __restrict__ b_out, float* __restrict__ e_out, int R, int heads) {
+                   const int* __restrict__ state_slot, float* __restrict__ m_state, float* a_out, float* b_out,
+                   float* __restrict__ e_out, int R, int heads) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
-    __shared__ float2 gates[GATE_WARPS][32];     // (f, i) of the stretch's tokens
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int item = blockIdx.x * GATE_WARPS + warp;
-    if (item >= R * heads) return;
-    const int r = item / heads, h = item - r * heads;
+    __shared__ float2 gates[32];     // (f, i) of the stretch's tokens
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x / heads, h = blockIdx.x - r * heads;
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     if (t0 >= t1) return;
+    const float bi = bias_i[h], bf = bias_f[h], inv_cap = 1.f / cap;
+    for (int t = t0 + threadIdx.x; t < t1; t += GATE_THREADS) {
+        const float* row = proj + (size_t)t * ld;
+        const size_t o = (size_t)t * heads + h;
+        b_out[o] = cap * tanhf((row[i_off + h] + bi) * inv_cap);
+        a_out[o] = log_sigmoid(cap * tanhf((row[f_off + h] + bf) * inv_cap));
+    }
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
     float* mp = m_state + (size_t)state_slot[r] * heads + h;
     float m = *mp;
-    const float bi = bias_i[h], bf = bias_f[h], inv_cap = 1.f / cap;
-    // the next stretch's projections travel while this stretch's chain runs
-    float zi = 0.f, zf = 0.f;
-    if (t0 + lane < t1) { const float* row = proj + (size_t)(t0 + lane) * ld; zi = row[i_off + h]; zf = row[f_off + h]; }
+    float gi = 0.f, gf = 0.f;
+    if (t0 + lane < t1) { const size_t o = (size_t)(t0 + lane) * heads + h; gf = a_out[o]; gi = b_out[o]; }
     for (int tb = t0; tb < t1; tb += 32) {
         const int t = tb + lane;
-        const float gi = cap * tanhf((zi + bi) * inv_cap);
-        const float gf = log_sigmoid(cap * tanhf((zf + bf) * inv_cap));
-        if (t + 32 < t1) { const float* row = proj + (size_t)(t + 32) * ld; zi = row[i_off + h]; zf = row[f_off + h]; }
+        const float my_f = gf, my_i = gi;
         __syncwarp();
-        gates[warp][lane] = make_float2(gf, gi);
+        gates[lane] = make_float2(gf, gi);
         __syncwarp();
+        if (t + 32 < t1) { const size_t o = (size_t)(t + 32) * heads + h; gf = a_out[o]; gi = b_out[o]; }   // the next stretch travels
         const int n = min(32, t1 - tb);
         float m_before = 0.f, m_after = 0.f;
         if (n == 32) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float2 g = gates[warp][j];
+                const float2 g = gates[j];
                 const float m_new = fmaxf(g.x + m, g.y);
                 if (j == lane) { m_before = m; m_after = m_new; }
                 m = m_new;
             }
         } else {
             for (int j = 0; j < n; ++j) {
-                const float2 g = gates[warp][j];
+                const float2 g = gates[j];
                 const float m_new = fmaxf(g.x + m, g.y);
                 if (j == lane) { m_before = m; m_after = m_new; }
                 m = m_new;
@@ -73,8 +78,8 @@ mlstm_gates_kernel(const float* __restrict__ proj, long long ld, int i_off, int 
         }
         if (t < t1) {
             const size_t o = (size_t)t * heads + h;
-            a_out[o] = expf(gf + m_before - m_after);
-            b_out[o] = expf(gi - m_after);
+            a_out[o] = expf(my_f + m_before - m_after);
+            b_out[o] = expf(my_i - m_after);
             e_out[o] = expf(-m_after);
         }
     }
@@ -113,7 +118,7 @@ BW_EXPORT int bw_mlstm_gates(const float* proj, long long ld, int i_off, int f_o
     if (R <= 0) return 0;
     if (heads <= 0 || !(cap > 0.f) || !bias_i || !bias_f || ld < (long long)i_off + heads || ld < (long long)f_off + heads)
         return BW_ERR_BAD_ARG;
-    bw::launch(mlstm_gates_kernel, dim3((R * heads + GATE_WARPS - 1) / GATE_WARPS), dim3(GATE_WARPS * 32), 0, (cudaStream_t)stream, proj, ld, i_off, f_off, bias_i,
+    bw::launch(mlstm_gates_kernel, dim3(R * heads), dim3(GATE_THREADS), 0, (cudaStream_t)stream, proj, ld, i_off, f_off, bias_i,
                bias_f, cap, cu_q, state_slot, m_state, a, b, e, R, heads);
     BW_LAUNCH_CHECK();
     return 0;
