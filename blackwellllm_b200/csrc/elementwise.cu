@@ -224,7 +224,7 @@ __global__ void scale_add_kernel(float* __restrict__ x, const float* __restrict_
 // sublayers read two norms of the same stream): x[t] += a[t] * ga + b[t] * gb (a == null: x stays as it is), then
 // o1[t] = x[t] / rms(x[t]) * w1 and (o2 != null) o2[t] = x[t] / rms(x[t]) * w2.  One block per row; every thread re-reads
 // only what it wrote itself; the order of the sum of squares depends on H and the block size alone.
-template <typename WT, typename OT>
+template <typename WT, typename OT, bool VEC>
 __global__ void scale_add_norm2_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ ga,
                                        const float* __restrict__ b, const float* __restrict__ gb,
                                        const WT* __restrict__ w1, const WT* __restrict__ w2, OT* __restrict__ o1,
@@ -234,23 +234,48 @@ __global__ void scale_add_norm2_kernel(float* __restrict__ x, const float* __res
     __shared__ float scratch[32];
     const size_t row = (size_t)blockIdx.x * H;
     float* xr = x + row;
+    constexpr int W = VEC ? 4 : 1;     // VEC: four channels a thread and access (H a multiple of 4, 16-byte aligned rows)
     float ss = 0.f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float v = xr[c];
-        if (a) {
-            float y = a[row + c] * ga[c];
-            if (b) y += b[row + c] * gb[c];
-            v += y;
-            xr[c] = v;
+    for (int c = threadIdx.x * W; c < H; c += blockDim.x * W) {
+        if constexpr (VEC) {
+            float4 v = load4(xr + c);
+            if (a) {
+                const float4 av = load4(a + row + c), g1 = load4(ga + c);
+                float4 y = make_float4(av.x * g1.x, av.y * g1.y, av.z * g1.z, av.w * g1.w);
+                if (b) {
+                    const float4 bv = load4(b + row + c), g2 = load4(gb + c);
+                    y.x += bv.x * g2.x; y.y += bv.y * g2.y; y.z += bv.z * g2.z; y.w += bv.w * g2.w;
+                }
+                v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
+                store4(xr + c, v);
+            }
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        } else {
+            float v = xr[c];
+            if (a) {
+                float y = a[row + c] * ga[c];
+                if (b) y += b[row + c] * gb[c];
+                v += y;
+                xr[c] = v;
+            }
+            ss = fmaf(v, v, ss);
         }
-        ss = fmaf(v, v, ss);
     }
     ss = bw::block_sum(ss, scratch) / (float)H;
     const float r1 = rsqrtf(ss + eps1), r2 = rsqrtf(ss + eps2);
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const float v = xr[c];
-        o1[row + c] = bw::from_f32<OT>(v * r1 * bw::to_f32(w1[c]));
-        if (o2) o2[row + c] = bw::from_f32<OT>(v * r2 * bw::to_f32(w2[c]));
+    for (int c = threadIdx.x * W; c < H; c += blockDim.x * W) {
+        if constexpr (VEC) {
+            const float4 v = load4(xr + c), g1 = load4(w1 + c);
+            store4(o1 + row + c, make_float4(v.x * r1 * g1.x, v.y * r1 * g1.y, v.z * r1 * g1.z, v.w * r1 * g1.w));
+            if (o2) {
+                const float4 g2 = load4(w2 + c);
+                store4(o2 + row + c, make_float4(v.x * r2 * g2.x, v.y * r2 * g2.y, v.z * r2 * g2.z, v.w * r2 * g2.w));
+            }
+        } else {
+            const float v = xr[c];
+            o1[row + c] = bw::from_f32<OT>(v * r1 * bw::to_f32(w1[c]));
+            if (o2) o2[row + c] = bw::from_f32<OT>(v * r2 * bw::to_f32(w2[c]));
+        }
     }
 }
 
@@ -648,9 +673,13 @@ BW_EXPORT int bw_scale_add_norm2(float* x, const float* a, const float* ga, cons
         (o2 != nullptr) != (w2 != nullptr))
         return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define BW_SAN(WT, OT) bw::launch((scale_add_norm2_kernel<WT, OT>), dim3(T), dim3(threads), 0, s, x, a, ga, b, gb, \
-        (const WT*)w1, (const WT*)w2, (OT*)o1, (OT*)o2, H, eps1, eps2)
+    const bool vec = H % 4 == 0 && (((uintptr_t)x | (uintptr_t)a | (uintptr_t)ga | (uintptr_t)b | (uintptr_t)gb | (uintptr_t)w1 |
+                                     (uintptr_t)w2 | (uintptr_t)o1 | (uintptr_t)o2) & 15) == 0;
+    const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
+#define BW_SAN(WT, OT) do { if (vec) bw::launch((scale_add_norm2_kernel<WT, OT, true>), dim3(T), dim3(threads), 0, s, x, a, ga, b, gb, \
+        (const WT*)w1, (const WT*)w2, (OT*)o1, (OT*)o2, H, eps1, eps2); \
+        else bw::launch((scale_add_norm2_kernel<WT, OT, false>), dim3(T), dim3(threads), 0, s, x, a, ga, b, gb, \
+        (const WT*)w1, (const WT*)w2, (OT*)o1, (OT*)o2, H, eps1, eps2); } while (0)
     if (w_type == BW_F32 && out_type == BW_F32) BW_SAN(float, float);
     else if (w_type == BW_F32 && out_type == BW_BF16) BW_SAN(float, bf16);
     else if (w_type == BW_BF16 && out_type == BW_F32) BW_SAN(bf16, float);
