@@ -388,14 +388,14 @@ def _vubotar_shape(width, heads, kv, hd, window, keep, m_heads, m_dk, m_dv, l_he
     attention, the same experts and the window as its mask block."""
     moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
     att = {"type": "attention", "mlp": moe,
-           "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0, "bias_max": 4 * window,
-                     "bias_rows": 32, "v_mix": True, "mask": {"size": window, "keep_first": keep}}}
-    mem = {"type": "mlstm", "mlp": moe, "mixer": {"heads": m_heads, "dim": m_dk, "vdim": m_dv, "gate_cap": 12.0}}
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 40.0, "bias_max": 4 * window,
+                     "bias_rows": 64, "v_mix": True, "mask": {"size": window, "keep_first": keep}}}
+    mem = {"type": "mlstm", "mlp": moe, "mixer": {"heads": m_heads, "dim": m_dk, "vdim": m_dv, "gate_cap": 15.0}}
     lat = {"type": "latent_attention", "mlp": moe,
            "mixer": {"heads": l_heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "kv_rank": l_rank, "q_rank": l_qrank,
                      "scale": (l_dim + l_rot) ** -0.5, "rot": {"base": 10000.0, "dims": l_rot}}}
     design = {"architecture": "Vubotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
-              "logit_scale": 1.0, "logit_softcap": 30.0, "layers": [mem, att, lat, att]}
+              "logit_scale": 1.0, "logit_softcap": 50.0, "layers": [mem, att, lat, att]}
     closest, dense = _gafulix_shape(width, heads, kv, hd, m_heads, m_dk, m_dv, experts, top, ff, window, vocab, 2)
     return design, dense, {"gafulix": closest}
 

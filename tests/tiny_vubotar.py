@@ -68,7 +68,7 @@ TENSOR = {
     "layers": [
         _attn(4, 1, 64, 64, 0.125, 16, 100, cap=None, size=50, keep=3, mlp=_moe(2, 1, 80)),
         _attn(4, 2, 64, 64, 0.1, 6, 40, cap=5.0, v_mix=True, mlp=_moe(8, 4, 32)),
-        _latent(2, 48, 64, 40, 64, 32, 0.11, 50000.0, mlp=_moe(4, 2, 64)),
+        _latent(2, 48, 64, 40, 64, 32, 0.11, 30000.0, mlp=_moe(4, 2, 64)),
         _mlstm(1, 160, 40, 15.0, mlp=None),
         _attn(2, 2, 64, 64, 0.2, 2, 5, cap=50.0, size=17, keep=40, v_mix=True, mlp=None),
     ],
@@ -87,11 +87,11 @@ OPEN = {
 }
 # one layer of each; head size 128; a window of one page exactly with more kept keys than that; a memory of 128 x 64
 BROAD = {
-    "architecture": "Vubotar", "vocab": 400, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 3.0},
-    "logit_scale": 0.5, "logit_softcap": 30.0,
+    "architecture": "Vubotar", "vocab": 400, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.5},
+    "logit_scale": 0.5, "logit_softcap": 25.0,
     "layers": [
         _attn(2, 1, 128, 128, 0.09, 24, 200, cap=10.0, size=64, keep=70, v_mix=True, mlp=_moe(4, 2, 128)),
-        _mlstm(2, 128, 64, 12.0, mlp=_moe(4, 3, 64)),
+        _mlstm(2, 128, 64, 9.0, mlp=_moe(4, 3, 64)),
         _latent(2, 64, 64, 128, 192, 96, 0.08, 10000.0, mlp=_moe(6, 2, 96)),
     ],
 }
