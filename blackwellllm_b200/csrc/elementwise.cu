@@ -228,36 +228,45 @@ template <typename WT, typename OT, bool VEC>
 __global__ void scale_add_norm2_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ ga,
                                        const float* __restrict__ b, const float* __restrict__ gb,
                                        const WT* __restrict__ w1, const WT* __restrict__ w2, OT* __restrict__ o1,
-                                       OT* __restrict__ o2, int H, float eps1, float eps2) {
+                                       OT* __restrict__ o2, const int* __restrict__ rows, int H, float eps1, float eps2) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     __shared__ float scratch[32];
-    const size_t row = (size_t)blockIdx.x * H;
+    // rows != null: only these rows are read (x stays as it is: the stream ends here), the results are dense
+    const size_t row = (size_t)(rows ? rows[blockIdx.x] : (int)blockIdx.x) * H, orow = (size_t)blockIdx.x * H;
     float* xr = x + row;
     constexpr int W = VEC ? 4 : 1;     // VEC: four channels a thread and access (H a multiple of 4, 16-byte aligned rows)
+    auto sum4 = [&](int c) {           // the new row's four channels from c on
+        float4 v = load4(xr + c);
+        if (a) {
+            const float4 av = load4(a + row + c), g1 = load4(ga + c);
+            float4 y = make_float4(av.x * g1.x, av.y * g1.y, av.z * g1.z, av.w * g1.w);
+            if (b) {
+                const float4 bv = load4(b + row + c), g2 = load4(gb + c);
+                y.x += bv.x * g2.x; y.y += bv.y * g2.y; y.z += bv.z * g2.z; y.w += bv.w * g2.w;
+            }
+            v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
+        }
+        return v;
+    };
+    auto sum1 = [&](int c) {
+        float v = xr[c];
+        if (a) {
+            float y = a[row + c] * ga[c];
+            if (b) y += b[row + c] * gb[c];
+            v += y;
+        }
+        return v;
+    };
     float ss = 0.f;
     for (int c = threadIdx.x * W; c < H; c += blockDim.x * W) {
         if constexpr (VEC) {
-            float4 v = load4(xr + c);
-            if (a) {
-                const float4 av = load4(a + row + c), g1 = load4(ga + c);
-                float4 y = make_float4(av.x * g1.x, av.y * g1.y, av.z * g1.z, av.w * g1.w);
-                if (b) {
-                    const float4 bv = load4(b + row + c), g2 = load4(gb + c);
-                    y.x += bv.x * g2.x; y.y += bv.y * g2.y; y.z += bv.z * g2.z; y.w += bv.w * g2.w;
-                }
-                v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
-                store4(xr + c, v);
-            }
+            const float4 v = sum4(c);
+            if (a && !rows) store4(xr + c, v);
             ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
         } else {
-            float v = xr[c];
-            if (a) {
-                float y = a[row + c] * ga[c];
-                if (b) y += b[row + c] * gb[c];
-                v += y;
-                xr[c] = v;
-            }
+            const float v = sum1(c);
+            if (a && !rows) xr[c] = v;
             ss = fmaf(v, v, ss);
         }
     }
@@ -265,16 +274,16 @@ __global__ void scale_add_norm2_kernel(float* __restrict__ x, const float* __res
     const float r1 = rsqrtf(ss + eps1), r2 = rsqrtf(ss + eps2);
     for (int c = threadIdx.x * W; c < H; c += blockDim.x * W) {
         if constexpr (VEC) {
-            const float4 v = load4(xr + c), g1 = load4(w1 + c);
-            store4(o1 + row + c, make_float4(v.x * r1 * g1.x, v.y * r1 * g1.y, v.z * r1 * g1.z, v.w * r1 * g1.w));
+            const float4 v = rows ? sum4(c) : load4(xr + c), g1 = load4(w1 + c);
+            store4(o1 + orow + c, make_float4(v.x * r1 * g1.x, v.y * r1 * g1.y, v.z * r1 * g1.z, v.w * r1 * g1.w));
             if (o2) {
                 const float4 g2 = load4(w2 + c);
-                store4(o2 + row + c, make_float4(v.x * r2 * g2.x, v.y * r2 * g2.y, v.z * r2 * g2.z, v.w * r2 * g2.w));
+                store4(o2 + orow + c, make_float4(v.x * r2 * g2.x, v.y * r2 * g2.y, v.z * r2 * g2.z, v.w * r2 * g2.w));
             }
         } else {
-            const float v = xr[c];
-            o1[row + c] = bw::from_f32<OT>(v * r1 * bw::to_f32(w1[c]));
-            if (o2) o2[row + c] = bw::from_f32<OT>(v * r2 * bw::to_f32(w2[c]));
+            const float v = rows ? sum1(c) : xr[c];
+            o1[orow + c] = bw::from_f32<OT>(v * r1 * bw::to_f32(w1[c]));
+            if (o2) o2[orow + c] = bw::from_f32<OT>(v * r2 * bw::to_f32(w2[c]));
         }
     }
 }
@@ -664,10 +673,10 @@ BW_EXPORT int bw_scale_add(float* x, const float* a, const float* ga, const floa
 }
 
 // x, a, b: float32 [T, H] (a, or b alone, may be null); ga, gb: float32 [H]; w1, w2: gains of w_type; o1, o2 (o2 may be
-// null): [T, H] of out_type.
+// null): [n, H] of out_type.  rows: null (n = all T rows, x is updated) or n row numbers (x is left as it is).
 BW_EXPORT int bw_scale_add_norm2(float* x, const float* a, const float* ga, const float* b, const float* gb, const void* w1,
-                                 const void* w2, int w_type, void* o1, void* o2, int out_type, int T, int H, float eps1,
-                                 float eps2, void* stream) {
+                                 const void* w2, int w_type, void* o1, void* o2, int out_type, const int* rows, int T, int H,
+                                 float eps1, float eps2, void* stream) {
     if (T <= 0) return 0;
     if (!x || !w1 || !o1 || H <= 0 || (a != nullptr) != (ga != nullptr) || (b != nullptr) != (gb != nullptr) || (b && !a) ||
         (o2 != nullptr) != (w2 != nullptr))
@@ -677,9 +686,9 @@ BW_EXPORT int bw_scale_add_norm2(float* x, const float* a, const float* ga, cons
                                      (uintptr_t)w2 | (uintptr_t)o1 | (uintptr_t)o2) & 15) == 0;
     const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
 #define BW_SAN(WT, OT) do { if (vec) bw::launch((scale_add_norm2_kernel<WT, OT, true>), dim3(T), dim3(threads), 0, s, x, a, ga, b, gb, \
-        (const WT*)w1, (const WT*)w2, (OT*)o1, (OT*)o2, H, eps1, eps2); \
+        (const WT*)w1, (const WT*)w2, (OT*)o1, (OT*)o2, rows, H, eps1, eps2); \
         else bw::launch((scale_add_norm2_kernel<WT, OT, false>), dim3(T), dim3(threads), 0, s, x, a, ga, b, gb, \
-        (const WT*)w1, (const WT*)w2, (OT*)o1, (OT*)o2, H, eps1, eps2); } while (0)
+        (const WT*)w1, (const WT*)w2, (OT*)o1, (OT*)o2, rows, H, eps1, eps2); } while (0)
     if (w_type == BW_F32 && out_type == BW_F32) BW_SAN(float, float);
     else if (w_type == BW_F32 && out_type == BW_BF16) BW_SAN(float, bf16);
     else if (w_type == BW_BF16 && out_type == BW_F32) BW_SAN(bf16, float);

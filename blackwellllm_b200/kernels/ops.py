@@ -1159,12 +1159,17 @@ def scale_add(stream: torch.Tensor, a: torch.Tensor, ga: torch.Tensor, b: Option
 
 
 def scale_add_norm2(stream: torch.Tensor, pending: Optional[tuple], w1: torch.Tensor, eps1: float,
-                    w2: Optional[torch.Tensor], eps2: float, out_dtype: torch.dtype):
+                    w2: Optional[torch.Tensor], eps2: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
     """One pass over the stream's rows: with ``pending`` = (a, ga, b, gb) (b and gb may be None) first
     ``stream += a * ga + b * gb`` as :func:`scale_add` makes it, then two RMS norms of the new rows, ``stream / rms *
-    w1`` and (``w2`` given) ``stream / rms * w2``, in ``out_dtype``.  Returns (h1, h2 or None)."""
+    w1`` and (``w2`` given) ``stream / rms * w2``, in ``out_dtype``.  Returns (h1, h2 or None).  ``rows`` (int32): only
+    these rows are made, and the stream is left as it is (the model's last norm on the rows whose logits are wanted)."""
     _dev(stream, "stream", torch.float32); _dev(w1, "w1")
     T, H = stream.shape
+    n = T
+    if rows is not None:
+        _dev(rows, "rows", torch.int32)
+        n = rows.numel()
     a = ga = b = gb = None
     if pending is not None:
         a, ga, b, gb = pending
@@ -1177,14 +1182,14 @@ def scale_add_norm2(stream: torch.Tensor, pending: Optional[tuple], w1: torch.Te
                 raise KernelError("scale_add_norm2: b must have the stream's shape, its gain the width")
     if w1.numel() != H or (w2 is not None and (w2.numel() != H or w2.dtype != w1.dtype)):
         raise KernelError("scale_add_norm2: the norms' gains must have the stream's width and one type")
-    h1 = torch.empty((T, H), dtype=out_dtype, device=stream.device)
-    h2 = torch.empty((T, H), dtype=out_dtype, device=stream.device) if w2 is not None else None
+    h1 = torch.empty((n, H), dtype=out_dtype, device=stream.device)
+    h2 = torch.empty((n, H), dtype=out_dtype, device=stream.device) if w2 is not None else None
     if w2 is not None:
         _dev(w2, "w2")
-    fn = _fn("elementwise", "bw_scale_add_norm2", [c_void_p] * 7 + [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
-                                                                  c_float, c_void_p])
+    fn = _fn("elementwise", "bw_scale_add_norm2", [c_void_p] * 7 + [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                                  c_float, c_float, c_void_p])
     _check(fn(_ptr(stream), _ptr(a), _ptr(ga), _ptr(b), _ptr(gb), _ptr(w1), _ptr(w2), _code(w1, "w1"), _ptr(h1), _ptr(h2),
-              _code(h1, "out"), T, H, float(eps1), float(eps2), _stream()), "scale_add_norm2")
+              _code(h1, "out"), _ptr(rows), n, H, float(eps1), float(eps2), _stream()), "scale_add_norm2")
     return h1, h2
 
 

@@ -68,6 +68,8 @@ class DecoderModel:
             self._ones = torch.ones(self.streams, dtype=torch.float32, device=ctx.device)
         elif any(ls.block == "hyper" for ls in config.layers):
             raise ValueError("'hyper' blocks need ModelConfig.streams")
+        from ..parts.norm import RMSNorm
+        self._plain_final_norm = type(self.final_norm) is RMSNorm and self.final_norm.offset == 0.0
         self._pos_freq = None
         pe = config.position_embedding
         if pe is not None:
@@ -177,6 +179,11 @@ class DecoderModel:
             y, mix, out_w = batch.extras.pop("hc_write", None) or (None, None, None)
             x = ops.hc_step(h, S, y, mix, out_w, in_w=self._ones, gain=self.final_norm.gain_f32(), eps=self.final_norm.eps,
                             rows=batch.logit_rows, out_dtype=self.ctx.dtype)
+        elif "scaled_sum" in batch.extras and self._plain_final_norm:
+            # the last block's open layer-scale sum and the model's norm, on the wanted rows only (the stream ends here)
+            ops.resolve_pending()
+            x, _ = ops.scale_add_norm2(h, batch.extras.pop("scaled_sum"), self.final_norm.weight, self.final_norm.eps, None, 0.0,
+                                       self.ctx.dtype, rows=batch.logit_rows)
         else:
             if "scaled_sum" in batch.extras:
                 ops.resolve_pending()

@@ -74,6 +74,11 @@ def test_layer_scale_sum_and_both_norms_in_one_pass(ops, out_dtype, T, H):
         assert (h2 is None) == (not two)
         if two:
             assert float((h2.double().cpu() - plain.rms_norm(want_x, w2.double(), 1e-3)).abs().max()) < tol * 4
+        if pending is True and T > 1:       # chosen rows: the stream stays, the rows' norms are those of the new rows
+            xs, pick = d(x.clone()), torch.tensor([T - 1, 0], dtype=torch.int32)
+            h1, _ = ops.scale_add_norm2(xs, pend, d(w1), 1e-5, None, 0.0, out_dtype, rows=d(pick))
+            assert torch.equal(xs.cpu(), x) and h1.shape == (2, H)
+            assert float((h1.double().cpu() - plain.rms_norm(want_x[[T - 1, 0]], w1.double(), 1e-5)).abs().max()) < tol * 4
 
 
 @pytest.mark.parametrize("T,H,ld", [(5, 24, 100), (40, 128, 131), (3, 64, 64)])
@@ -307,6 +312,89 @@ def test_matrix_memory_keeps_a_far_token(ops):
         last = o[-1].cpu()
         ratio = float(last[0] / last[dv])                 # S^T q over n . q: the value the query reads
         assert abs(ratio - (1.0 if closed else 5.0)) < 0.2, (closed, ratio)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,d_,dr,dv,rank,qr,page", [(2, 16, 8, 24, 40, 24, 8), (3, 8, 16, 8, 24, 10, 16), (4, 32, 32, 48, 96, 64, 16),
+                                                     (20, 12, 12, 20, 24, 16, 32), (2, 16, 16, 24, 272, 40, 16), (17, 8, 8, 8, 24, 8, 8)])
+def test_latent_attention_with_latent_queries_paired_rotation_and_gate(ops, dtype, H, d_, dr, dv, rank, qr, page):
+    """The mixer alone against the plain function: a prompt in two portions and then single tokens, next to another
+    request; the cache holds one row of rank + rot_dim channels per token; 20 heads share it (two groups on the tensor
+    cores) or 17 (one call); a latent row wider than the tensor-core kernels' head sizes."""
+    from blackwellllm_b200.config.specs import LatentAttentionSpec, RopeSpec
+    from blackwellllm_b200.parts import BuildContext, build_mixer
+    from test_kernels_gpu import FakeBatch
+    W, eps, L = 64, 1e-5, 75
+    names = (("dq", "dq"), ("dq_norm", "dq.norm"), ("uq", "uq"), ("dkv", "dkv"), ("dkv_norm", "dkv.norm"), ("uk", "uk"), ("uv", "uv"),
+             ("g", "g"), ("o", "o"))
+    spec = LatentAttentionSpec(num_heads=H, head_dim=d_, rot_dim=dr, v_head_dim=dv, kv_rank=rank, norm_eps=eps,
+                               position=RopeSpec(theta=700.0, rotary_dim=dr, scaling=None, interleaved=True),
+                               softmax_scale=0.2, window=None, sink=False, names=names, q_rank=qr, output_gate=True)
+    mixer = build_mixer(spec, W, BuildContext(DEV, dtype))
+    t = {p.name: rnd(*p.shape, seed=i + 1, scale=0.3 if len(p.shape) > 1 else 1.0).to(dtype) for i, p in enumerate(mixer.param_specs())}
+    for n in ("dkv.norm", "dq.norm"):
+        t[n] = (1.0 + 0.3 * t[n].float()).to(dtype)
+    t["uq"] = (t["uq"].float() * 3.0).to(dtype)
+    mixer.bind({k: d(v if len(v.shape) > 1 else v.float()) for k, v in t.items()})
+    rq = mixer.cache_request()
+    assert rq.single_plane and rq.num_kv_heads == 1 and rq.head_dim >= rank + dr
+    xs = {0: rnd(L, W, seed=50).to(dtype), 1: rnd(30, W, seed=51).to(dtype)}
+    m = {"heads": H, "dim": d_, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "q_rank": qr, "scale": 0.2, "rot": {"base": 700.0, "dims": dr}}
+    want = {r: plain.latent_attention(x.double(), {k: v.double() for k, v in t.items()}, m, eps) for r, x in xs.items()}
+    n_pages = -(-L // page) + -(-30 // page)
+    pool = torch.full((1, n_pages, 1, page, rq.head_dim), float("nan"), dtype=dtype, device=DEV)
+
+    class View:
+        group, k_pages, v_pages, page_size = 0, pool[0], pool[0], page
+    table = torch.full((2, -(-L // page)), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(9)).tolist()
+    for r, n in ((0, L), (1, 30)):
+        for b in range(-(-n // page)):
+            table[r, b] = perm.pop()
+    got = {0: [], 1: []}
+    at = {0: 0, 1: 0}
+    steps = [[(0, 33), (1, 2)], [(1, 1), (0, 30)]] + [[(0, 1), (1, 1)] for _ in range(12)]
+    for step in steps:
+        batch = FakeBatch([n for _, n in step], [at[r] + n for r, n in step])
+        batch.block_tables = {0: d(table[[r for r, _ in step]])}
+        x = torch.cat([xs[r][at[r]:at[r] + n] for r, n in step])
+        res = torch.zeros(x.shape[0], W, device=DEV)
+        mixer.forward(d(x), res, batch, View)
+        ops.resolve_pending()
+        o = 0
+        for r, n in step:
+            got[r].append(res[o:o + n].cpu().double())
+            o += n
+            at[r] += n
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    for r in (0, 1):
+        g = torch.cat(got[r])
+        assert float((g - want[r][:g.shape[0]]).abs().max()) <= tol * float(want[r].abs().max()), r
+
+
+@pytest.mark.parametrize("E,top,F,H", [(8, 3, 32, 64), (2, 2, 44, 50), (5, 1, 48, 64), (16, 4, 64, 128)])
+def test_routed_feed_forward_chooses_by_score_plus_correction(ops, E, top, F, H):
+    """float32: every row equals the plain function's; a correction large enough to overturn the scores' order decides
+    the choice while the weights stay the uncorrected scores over their sum."""
+    from blackwellllm_b200.config.specs import RoutedFFNSpec
+    from blackwellllm_b200.parts import BuildContext, build_ffn
+    from test_kernels_gpu import FakeBatch
+    spec = RoutedFFNSpec(num_experts=E, top_k=top, expert_size=F, score="sigmoid", renormalize=True, scale_input=False,
+                         router_name="router", expert_names=("e{e}.", "gate", "up", "down"), choice_bias="correction", renorm_eps=1e-20)
+    ffn = build_ffn(spec, H, BuildContext(DEV, torch.float32))
+    t = {p.name: rnd(*p.shape, seed=i + 3, scale=0.3) for i, p in enumerate(ffn.param_specs())}
+    t["correction"] = rnd(E, seed=77, scale=2.0)
+    ffn.bind({k: d(v) for k, v in t.items()})
+    f = {"router": {"experts": E, "top": top}, "expert": {"ff": F}}
+    for T in (1, 7, 200):
+        x = rnd(T, H, seed=T)
+        want = plain.routed_ffn(x.double(), {k: v.double() for k, v in t.items()}, f)
+        out = torch.zeros(T, H, device=DEV)
+        ffn.forward(d(x), out, FakeBatch([T], [T]), accumulate=False)
+        assert float((out.double().cpu() - want).abs().max()) <= 2e-5 * float(want.abs().max()), T
+        without = plain.routed_ffn(x.double(), dict({k: v.double() for k, v in t.items()}, correction=torch.zeros(E, dtype=F64)), f)
+        if top < E:
+            assert float((without - want).abs().max()) > 1e-3 * float(want.abs().max())
 
 
 # =============================================================================== whole models through the engine
