@@ -366,7 +366,13 @@ def test_latent_attention_with_latent_queries_paired_rotation_and_gate(ops, dtyp
             got[r].append(res[o:o + n].cpu().double())
             o += n
             at[r] += n
-XX, [(8, 3, 32, 64), (2, 2, 44, 50), (5, 1, 48, 64), (16, 4, 64, 128)])
+    tol = 2e-5 if dtype == torch.float32 else 4e-2
+    for r in (0, 1):
+        g = torch.cat(got[r])
+        assert float((g - want[r][:g.shape[0]]).abs().max()) <= tol * float(want[r].abs().max()), r
+
+
+@pytest.mark.parametrize("E,top,F,H", [(8, 3, 32, 64), (2, 2, 44, 50), (5, 1, 48, 64), (16, 4, 64, 128)])
 def test_routed_feed_forward_chooses_by_score_plus_correction(ops, E, top, F, H):
     """float32: every row equals the plain function's; a correction large enough to overturn the scores' order decides
     the choice while the weights stay the uncorrected scores over their sum."""
