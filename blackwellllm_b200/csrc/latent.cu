@@ -61,12 +61,17 @@ latent_prep_kernel(const float* __restrict__ qsrc, long long q_ld, int q_off, co
     }
 }
 
+// An output gate on a per-head product's result: sigmoid(gate[t, h * n_out + o]) (float32 rows g_ld apart), 1 without a gate.
+__device__ __forceinline__ float head_gate(const float* __restrict__ gate, long long g_ld, int t, int h, int n_out, int o) {
+    return gate ? 1.f / (1.f + expf(-gate[(size_t)t * g_ld + (size_t)h * n_out + o])) : 1.f;
+}
+
 // y[t, h * y_hs + o] = sum_i x[t, h * x_hs + i] * w[h, o, i]:  tiles of 32 tokens x 64 outputs, 32 inner values at a time.
 constexpr int HT = 32, HO = 64, HK = 32;
 template <typename XT, typename WT, typename YT>
 __global__ void __launch_bounds__(256)
 headwise_linear_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const WT* __restrict__ w, YT* __restrict__ y,
-                       long long ldy, int y_hs, int T, int n_in, int n_out) {
+                       long long ldy, int y_hs, int T, int n_in, int n_out, const float* __restrict__ gate, long long g_ld) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     __shared__ float xs[HT][HK + 1];
@@ -106,7 +111,7 @@ headwise_linear_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int o = o0 + tx + 16 * j;
-            if (o < n_out) y[(size_t)t * ldy + (size_t)h * y_hs + o] = bw::from_f32<YT>(acc[i][j]);
+            if (o < n_out) y[(size_t)t * ldy + (size_t)h * y_hs + o] = bw::from_f32<YT>(acc[i][j] * head_gate(gate, g_ld, t, h, n_out, o));
         }
     }
 }
@@ -129,7 +134,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 template <typename XT>
 __global__ void __launch_bounds__(128)
 headwise_mma_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const bf16* __restrict__ w, bf16* __restrict__ y,
-                    long long ldy, int y_hs, int T, int n_in, int n_out, int vec) {
+                    long long ldy, int y_hs, int T, int n_in, int n_out, int vec, const float* __restrict__ gate, long long g_ld) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     __shared__ __align__(16) uint8_t xs[MT * MROW];
@@ -201,11 +206,16 @@ headwise_mma_kernel(const XT* __restrict__ x, long long ldx, int x_hs, const bf1
 #pragma unroll
         for (int j = 0; j < MO / 8; ++j) {
             const int o = o0 + j * 8 + 2 * (lane & 3);
+            float r0 = acc[j][2 * half], r1 = acc[j][2 * half + 1];
+            if (gate) {
+                if (o < n_out) r0 *= head_gate(gate, g_ld, t, h, n_out, o);
+                if (o + 1 < n_out) r1 *= head_gate(gate, g_ld, t, h, n_out, o + 1);
+            }
             if (pairs && o + 1 < n_out) {
-                *reinterpret_cast<uint32_t*>(dst + o) = bw::pack_bf16x2(acc[j][2 * half], acc[j][2 * half + 1]);
+                *reinterpret_cast<uint32_t*>(dst + o) = bw::pack_bf16x2(r0, r1);
             } else {
-                if (o < n_out) dst[o] = __float2bfloat16_rn(acc[j][2 * half]);
-                if (o + 1 < n_out) dst[o + 1] = __float2bfloat16_rn(acc[j][2 * half + 1]);
+                if (o < n_out) dst[o] = __float2bfloat16_rn(r0);
+                if (o + 1 < n_out) dst[o + 1] = __float2bfloat16_rn(r1);
             }
         }
     }
@@ -247,23 +257,26 @@ BW_EXPORT int bw_latent_prep(const float* qsrc, long long q_ld, int q_off, const
 
 // x: rows ldx apart, head h's n_in inputs at column h * x_hs; w [H, n_out, n_in]; y: rows ldy apart, head h's n_out
 // outputs at column h * y_hs.  Types: x float32 or bfloat16; w and y float32 or bfloat16 (the same for both).
+// gate: null, or float32 rows g_ld apart with H * n_out values: the result is multiplied by sigmoid(gate[t, h * n_out + o])
+// before it is rounded and written.
 BW_EXPORT int bw_headwise_linear(const void* x, int x_type, long long ldx, int x_hs, const void* w, int w_type, void* y,
-                                 int y_type, long long ldy, int y_hs, int T, int H, int n_in, int n_out, void* stream) {
+                                 int y_type, long long ldy, int y_hs, int T, int H, int n_in, int n_out, const float* gate,
+                                 long long g_ld, void* stream) {
     if (T <= 0) return 0;
-    if (H <= 0 || n_in <= 0 || n_out <= 0 || H > 65535) return BW_ERR_BAD_ARG;
+    if (H <= 0 || n_in <= 0 || n_out <= 0 || H > 65535 || (gate && g_ld < (long long)H * n_out)) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((T + HT - 1) / HT, (n_out + HO - 1) / HO, H);
 #define BW_HW(XT, WT, YT) bw::launch((headwise_linear_kernel<XT, WT, YT>), grid, dim3(256), 0, s, (const XT*)x, ldx, x_hs, \
-        (const WT*)w, (YT*)y, ldy, y_hs, T, n_in, n_out)
+        (const WT*)w, (YT*)y, ldy, y_hs, T, n_in, n_out, gate, g_ld)
     const dim3 mgrid((T + MT - 1) / MT, (n_out + MO - 1) / MO, H);
     // 16-byte loads: 8 inner values of a row at a time, every row starting on a 16-byte boundary
     const int xe = x_type == BW_F32 ? 4 : 8;      // elements of x in 16 bytes
     const int vec = n_in % 8 == 0 && ldx % xe == 0 && x_hs % xe == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
     if (x_type == BW_F32 && w_type == BW_F32 && y_type == BW_F32) BW_HW(float, float, float);
     else if (x_type == BW_F32 && w_type == BW_BF16 && y_type == BW_BF16)      // bfloat16 weights and results: the tensor cores
-        bw::launch((headwise_mma_kernel<float>), mgrid, dim3(128), 0, s, (const float*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec);
+        bw::launch((headwise_mma_kernel<float>), mgrid, dim3(128), 0, s, (const float*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec, gate, g_ld);
     else if (x_type == BW_BF16 && w_type == BW_BF16 && y_type == BW_BF16)
-        bw::launch((headwise_mma_kernel<bf16>), mgrid, dim3(128), 0, s, (const bf16*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec);
+        bw::launch((headwise_mma_kernel<bf16>), mgrid, dim3(128), 0, s, (const bf16*)x, ldx, x_hs, (const bf16*)w, (bf16*)y, ldy, y_hs, T, n_in, n_out, vec, gate, g_ld);
     else return BW_ERR_UNSUPPORTED;
 #undef BW_HW
     BW_LAUNCH_CHECK();

@@ -1372,20 +1372,27 @@ def latent_prep(proj: torch.Tensor, q_off: int, kv_off: int, batch, block_table:
     return q
 
 
-def headwise_linear(x: torch.Tensor, x_off: int, x_hs: int, w: torch.Tensor, y: torch.Tensor, y_off: int, y_hs: int) -> torch.Tensor:
+def headwise_linear(x: torch.Tensor, x_off: int, x_hs: int, w: torch.Tensor, y: torch.Tensor, y_off: int, y_hs: int,
+                    gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``y[t, y_off + h * y_hs + o] = sum_i x[t, x_off + h * x_hs + i] * w[h, o, i]`` for every head h: one small
-    product per head.  w [H, n_out, n_in]; x float32 or bfloat16, w and y of one type (float32 sums in a fixed order)."""
+    product per head.  w [H, n_out, n_in]; x float32 or bfloat16, w and y of one type (float32 sums in a fixed order).
+    ``gate`` (float32 [T, H * n_out], possibly a range of columns of a wider tensor): the result is multiplied by
+    sigmoid(gate[t, h * n_out + o]) before it is rounded and written."""
     _dev(x, "x", contiguous=False); _dev(w, "w"); _dev(y, "y", contiguous=False)
     H, n_out, n_in = w.shape
     T = x.shape[0]
+    if gate is not None:
+        _dev(gate, "gate", torch.float32, contiguous=False)
+        if gate.shape != (T, H * n_out) or gate.stride(1) != 1:
+            raise KernelError("headwise_linear: the gate must be float32 [T, H * n_out] with contiguous rows")
     if (x.dim() != 2 or y.dim() != 2 or y.shape[0] != T or x.stride(1) != 1 or y.stride(1) != 1
             or x_off + (H - 1) * x_hs + n_in > x.shape[1] or y_off + (H - 1) * y_hs + n_out > y.shape[1]):
         raise KernelError("headwise_linear: x [T, >= x_off + (H - 1) x_hs + n_in], y [T, >= y_off + (H - 1) y_hs + n_out]")
     fn = _fn("latent", "bw_headwise_linear", [c_void_p, c_int, c_ll, c_int, c_void_p, c_int, c_void_p, c_int, c_ll, c_int,
-                                              c_int, c_int, c_int, c_int, c_void_p])
+                                              c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p])
     _check(fn(c_void_p(x.data_ptr() + x_off * x.element_size()), _code(x, "x"), x.stride(0), int(x_hs), _ptr(w), _code(w, "w"),
               c_void_p(y.data_ptr() + y_off * y.element_size()), _code(y, "y"), y.stride(0), int(y_hs), T, H, n_in, n_out,
-              _stream()), "headwise_linear")
+              _ptr(gate), gate.stride(0) if gate is not None else 0, _stream()), "headwise_linear")
     return y
 
 

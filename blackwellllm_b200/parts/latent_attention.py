@@ -21,8 +21,8 @@ attention's output; the output projection into the stream.  The rotation is the 
 
 Options of the spec: ``q_rank`` (the queries come through a latent of their own: the first product also makes
 ``W_dq x``, an RMS norm with a gain follows, then ``W_uq`` makes the queries); ``output_gate`` (the concatenated heads'
-outputs times ``sigmoid(W_g x)``, W_g's rows riding in the first product; the gate is applied after the per-head value
-product, in place); a rotary encoding that pairs channel 2j with channel 2j + 1.
+outputs times ``sigmoid(W_g x)``, W_g's rows riding in the first product; the gate is applied in the per-head value
+product's epilogue); a rotary encoding that pairs channel 2j with channel 2j + 1.
 """
 from __future__ import annotations
 
@@ -134,10 +134,11 @@ class LatentAttention(Mixer):
             ops.headwise_linear(qs, h0 * (d + dr), d + dr, self.uk_t[h0:h0 + n], q, 0, self.dpad)
             o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, bt, n, self.window, self.scale, None,
                                     None if self.sink is None else self.sink[h0:h0 + n], None)
-            ops.headwise_linear(o, 0, self.dpad, self.uv[h0:h0 + n], y, h0 * self.dv, self.dv)
-        if self.gated:
-            g_off = kv_off + rank + dr
-            ops.sigmoid_gate(y, proj[:, g_off:g_off + H * self.dv], H, self.dv)
+            gate = None
+            if self.gated:      # the gate's sigmoid multiplies the per-head value product's result as it is written
+                g_off = kv_off + rank + dr + h0 * self.dv
+                gate = proj[:, g_off:g_off + n * self.dv]
+            ops.headwise_linear(o, 0, self.dpad, self.uv[h0:h0 + n], y, h0 * self.dv, self.dv, gate=gate)
         if accumulate:
             self.o.add_to(y, residual)
         elif accumulate is None:
