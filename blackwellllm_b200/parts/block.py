@@ -274,6 +274,7 @@ class ParallelBlock(PreNormBlock):
         if self.shift_name is not None:
             if not owns_cache:
                 raise ops.KernelError("a block with a token shift owns its state: it cannot run on another run's cache")
+            flush_scaled_sum(residual, batch)
             mixer_cache, state = (cache[0], cache[1]) if len(cache) == 2 else (None, cache[0])
             h, hs = ops.rmsnorm_shift(residual, self.mixer_norm.gain_f32(), self.shift, state.state, batch,
                                       self.mixer_norm.eps, self.ctx.dtype, want_h=self.ffn is not None)
